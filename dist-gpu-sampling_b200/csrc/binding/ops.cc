@@ -1,0 +1,511 @@
+// PyTorch operator layer: torch.classes.dgs_classes.ChunkTensor and
+// torch.ops.dgs_ops.* with the reference's schemas (src/pybind.cc:11-38,
+// src/cuda/dgs_ops.h:10-50), implemented as a thin host layer over the C ABI
+// of include/dgs_b200.h.  This is the only file that sees torch types; every
+// kernel launch goes through an extern "C" entry point.
+//
+// Conventions kept from the reference: one process per GPU, tensors returned
+// on the current CUDA device, ChunkTensor construction/destruction collective
+// over the communicator set by _CAPI_set_nccl (optional here: without it the
+// process is a single-rank group).  Conventions changed: kernels run on
+// torch's current stream (the reference uses the legacy default stream, which
+// is also torch's default), and every failure surfaces as a c10::Error --
+// nothing calls exit()/abort() (src/dgs_headers.h:11-45).
+#include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAGeneratorImpl.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime.h>
+#include <torch/custom_class.h>
+#include <torch/script.h>
+
+#include <mutex>
+#include <tuple>
+#include <vector>
+
+#include "../../../include/dgs_b200.h"
+
+namespace dgs {
+namespace {
+
+#define DGS_CHECK_RC(expr)                                                        \
+  do {                                                                            \
+    int rc__ = (expr);                                                            \
+    TORCH_CHECK(rc__ == DGS_OK, "dgs: ", dgs_last_error(), " (code ", rc__, ")"); \
+  } while (0)
+
+#define CHECK_CUDA(x) TORCH_CHECK((x).device().is_cuda(), #x " must be a CUDA tensor")
+
+// ---- pinned words the kernels write data-dependent sizes / status into ----
+struct HostWords {
+  int64_t* sizes = nullptr;  // [8]
+  int32_t* status = nullptr; // [1]
+};
+
+HostWords& host_words() {
+  static HostWords w;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    TORCH_CHECK(cudaHostAlloc(&p, 128, cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess,
+                "dgs: cannot allocate pinned status words");
+    std::memset(p, 0, 128);
+    w.sizes = static_cast<int64_t*>(p);
+    w.status = reinterpret_cast<int32_t*>(static_cast<char*>(p) + 64);
+  });
+  return w;
+}
+
+// Out-of-range ids / full tables are recorded by the kernels instead of
+// trapping; report them at the next point where the host looks.
+void check_status(const char* where) {
+  HostWords& w = host_words();
+  const int32_t st = *static_cast<volatile int32_t*>(w.status);
+  if (st != 0) {
+    *w.status = 0;
+    TORCH_CHECK(false, "dgs: a kernel reported ",
+                st == DGS_ERR_RANGE ? "an out-of-range id"
+                                    : (st == DGS_ERR_TABLE_FULL ? "a full hash table" : "an error"),
+                " (code ", st, "), noticed in ", where);
+  }
+}
+
+cudaStream_t current_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+void sync_stream() {
+  TORCH_CHECK(cudaStreamSynchronize(current_stream()) == cudaSuccess, "dgs: stream synchronisation failed: ",
+              cudaGetErrorString(cudaGetLastError()));
+}
+
+bool is_id64(const torch::Tensor& t, const char* what) {
+  TORCH_CHECK(t.scalar_type() == torch::kInt64 || t.scalar_type() == torch::kInt32,
+              "ID can only be int32 or int64 (", what, ")");
+  return t.scalar_type() == torch::kInt64;
+}
+
+size_t dtype_size(torch::ScalarType t) {
+  // the types ChunkTensor accepts (src/chunk_tensor.cc:15-30)
+  switch (t) {
+    case torch::kInt32: return 4;
+    case torch::kInt64: return 8;
+    case torch::kFloat: return 4;
+    case torch::kDouble: return 8;
+    case torch::kBool: return 1;
+    default: TORCH_CHECK(false, "ChunkTensor: unsupported dtype ", t);
+  }
+}
+
+dgs_chunk_desc plain_desc(const torch::Tensor& t) {
+  dgs_chunk_desc d;
+  std::memset(&d, 0, sizeof(d));
+  d.total = d.threshold = d.each = t.numel();
+  d.num_parts = 1;
+  d.local_rank = 0;
+  d.esz = static_cast<int32_t>(t.element_size());
+  d.dev[0] = t.data_ptr();
+  return d;
+}
+
+torch::Tensor byte_scratch(size_t bytes, const torch::Device& dev) {
+  return torch::empty({static_cast<int64_t>(bytes)}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
+}
+
+// (seed, offset) from torch's default CUDA generator, so torch.manual_seed
+// controls sampling; each call consumes one offset step.
+std::pair<uint64_t, uint64_t> next_rng() {
+  auto gen = at::get_generator_or_default<at::CUDAGeneratorImpl>(
+      c10::nullopt, at::cuda::detail::getDefaultCUDAGenerator());
+  std::lock_guard<std::mutex> lock(gen->mutex_);
+  const uint64_t seed = gen->current_seed();
+  const uint64_t offset = gen->get_offset();
+  gen->set_offset(offset + 4);
+  return {seed, offset};
+}
+
+}  // namespace
+
+// ===========================================================================
+class ChunkTensor : public torch::CustomClassHolder {
+ public:
+  ChunkTensor(std::vector<int64_t> shapes, torch::ScalarType dtype, int64_t capacity_per_gpu) {
+    TORCH_CHECK(shapes.size() == 1 || shapes.size() == 2, "ChunkTensor: shape must have 1 or 2 dims");
+    TORCH_CHECK(capacity_per_gpu >= 0, "ChunkTensor: capacity_per_gpu must be >= 0");
+    dtype_ = dtype;
+    const size_t esz = dtype_size(dtype);
+    DGS_CHECK_RC(dgs_device_check());
+    DGS_CHECK_RC(dgs_store_create(shapes.data(), static_cast<int32_t>(shapes.size()),
+                                  static_cast<int32_t>(esz), capacity_per_gpu, &store_));
+    DGS_CHECK_RC(dgs_store_desc(store_, &desc_));
+    elem_stride_ = dgs_store_elem_stride(store_);
+    TORCH_CHECK(cudaGetDevice(&device_) == cudaSuccess, "ChunkTensor: no current CUDA device");
+  }
+  ~ChunkTensor() override {
+    if (store_ != nullptr) dgs_store_destroy(store_);
+  }
+
+  torch::Tensor GetHostTensor() {
+    void* p = nullptr;
+    int64_t n = 0;
+    DGS_CHECK_RC(dgs_store_host_view(store_, &p, &n));
+    auto opt = torch::TensorOptions().device(torch::kCPU).dtype(dtype_);
+    return n > 0 ? torch::from_blob(p, {n}, opt) : torch::empty({0}, opt);
+  }
+
+  torch::Tensor GetSubDeviceTensor() {
+    void* p = nullptr;
+    int64_t n = 0;
+    DGS_CHECK_RC(dgs_store_local_view(store_, &p, &n));
+    auto opt = torch::TensorOptions().device(torch::Device(torch::kCUDA, device_)).dtype(dtype_);
+    return n > 0 ? torch::from_blob(p, {n}, opt) : torch::empty({0}, opt);
+  }
+
+  torch::Tensor IndexClass(torch::Tensor index, int32_t location_class) {
+    CHECK_CUDA(index);
+    check_status("_CAPI_index");
+    const bool ids64 = is_id64(index, "index");
+    c10::cuda::CUDAGuard guard(index.device());
+    index = index.contiguous();
+    const int64_t n = index.numel();
+    torch::Tensor out =
+        torch::empty({n, elem_stride_}, torch::TensorOptions().dtype(dtype_).device(index.device()));
+    DGS_CHECK_RC(dgs_gather_rows(&desc_, location_class, index.data_ptr(), ids64, n, elem_stride_,
+                                 out.data_ptr(), host_words().status, current_stream()));
+    return out;
+  }
+  torch::Tensor Index(torch::Tensor index) { return IndexClass(index, DGS_CLASS_ANY); }
+  torch::Tensor LocalIndex(torch::Tensor index) { return IndexClass(index, DGS_CLASS_LOCAL); }
+  torch::Tensor RemoteIndex(torch::Tensor index) { return IndexClass(index, DGS_CLASS_REMOTE); }
+  torch::Tensor HostIndex(torch::Tensor index) { return IndexClass(index, DGS_CLASS_HOST); }
+
+  std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> SplitIndex(torch::Tensor index) {
+    CHECK_CUDA(index);
+    check_status("_CAPI_split_index");
+    const bool ids64 = is_id64(index, "index");
+    c10::cuda::CUDAGuard guard(index.device());
+    index = index.contiguous().view({-1});
+    const int64_t n = index.numel();
+    torch::Tensor out = torch::empty_like(index);
+    const size_t sb = dgs_split_index_scratch_bytes(n);
+    torch::Tensor scratch = byte_scratch(sb, index.device());
+    int64_t* counts = host_words().sizes;
+    DGS_CHECK_RC(dgs_split_index(&desc_, index.data_ptr(), ids64, n, elem_stride_, out.data_ptr(), counts,
+                                 scratch.data_ptr(), sb, current_stream()));
+    sync_stream();
+    const int64_t nl = counts[0], nr = counts[1], nh = counts[2];
+    TORCH_CHECK(nl + nr + nh == n, "dgs: split_index lost ids");
+    return std::make_tuple(out.narrow(0, 0, nl), out.narrow(0, nl, nr), out.narrow(0, nl + nr, nh));
+  }
+
+  void LoadFromTensor(torch::Tensor data) {
+    // argument checks of src/chunk_tensor.cc:174-181
+    dgs_chunk_desc d = desc_;
+    TORCH_CHECK(data.device().is_cpu(), "_CAPI_load_from_tensor: data must be a CPU tensor");
+    TORCH_CHECK(data.scalar_type() == dtype_, "_CAPI_load_from_tensor: dtype mismatch");
+    TORCH_CHECK(data.is_contiguous(), "_CAPI_load_from_tensor: data must be contiguous");
+    TORCH_CHECK(data.numel() == d.total, "_CAPI_load_from_tensor: shape mismatch");
+    TORCH_CHECK(data.dim() == 1 || (data.dim() == 2 && data.size(1) == elem_stride_),
+                "_CAPI_load_from_tensor: shape mismatch");
+    DGS_CHECK_RC(dgs_store_load(store_, data.data_ptr(), data.numel()));
+  }
+
+  const dgs_chunk_desc& desc() const { return desc_; }
+  torch::ScalarType dtype() const { return dtype_; }
+
+ private:
+  dgs_store* store_ = nullptr;
+  dgs_chunk_desc desc_;
+  torch::ScalarType dtype_;
+  int64_t elem_stride_ = 1;
+  int device_ = 0;
+};
+
+// ===========================================================================
+// sampling
+// ===========================================================================
+namespace {
+
+constexpr int64_t kOneShotOutputBytes = int64_t(1) << 28;  // over-allocate n*k up to 256 MB
+
+std::tuple<torch::Tensor, torch::Tensor> sample_impl(torch::Tensor seeds, const dgs_chunk_desc& indptr,
+                                                      torch::ScalarType indptr_dtype,
+                                                      const dgs_chunk_desc& indices,
+                                                      torch::ScalarType indices_dtype,
+                                                      const dgs_chunk_desc* probs, int64_t k, bool replace) {
+  CHECK_CUDA(seeds);
+  check_status("sample_neighbors");
+  TORCH_CHECK(k >= 0, "num_picks must be >= 0");
+  const bool ids64 = is_id64(seeds, "seeds");
+  TORCH_CHECK(seeds.scalar_type() == indptr_dtype && seeds.scalar_type() == indices_dtype,
+              "seeds, indptr and indices must share one id type");
+  c10::cuda::CUDAGuard guard(seeds.device());
+  seeds = seeds.contiguous().view({-1});
+  const int64_t n = seeds.numel();
+  auto opt = seeds.options();
+  cudaStream_t stream = current_stream();
+  HostWords& w = host_words();
+  const auto rng = next_rng();
+
+  const size_t pb = dgs_sample_plan_bytes(n);
+  torch::Tensor plan = byte_scratch(pb, seeds.device());
+  const int64_t esz = ids64 ? 8 : 4;
+  const bool one_shot = n * k * 2 * esz <= kOneShotOutputBytes;
+
+  auto run = [&](torch::Tensor& row, torch::Tensor& col, int64_t cap, int64_t* nnz) {
+    if (probs == nullptr)
+      DGS_CHECK_RC(dgs_sample_uniform(&indices, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(),
+                                      rng.first, rng.second, row.data_ptr(), col.data_ptr(), cap, nnz,
+                                      nullptr, w.status, stream));
+    else
+      DGS_CHECK_RC(dgs_sample_weighted(&indices, probs, seeds.data_ptr(), ids64, n, k, replace,
+                                       plan.data_ptr(), rng.first, rng.second, row.data_ptr(),
+                                       col.data_ptr(), cap, nnz, nullptr, w.status, stream));
+  };
+
+  torch::Tensor row, col;
+  int64_t nnz = 0;
+  if (one_shot) {
+    // everything is enqueued before the host waits once for the size
+    const int64_t cap = n * k;
+    row = torch::empty({cap}, opt);
+    col = torch::empty({cap}, opt);
+    DGS_CHECK_RC(dgs_sample_plan(&indptr, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), nullptr,
+                                 w.status, stream));
+    run(row, col, cap, w.sizes);
+    sync_stream();
+    nnz = w.sizes[0];
+    check_status("sample_neighbors");
+    TORCH_CHECK(nnz >= 0 && nnz <= cap, "dgs: sampler returned an impossible size");
+    return std::make_tuple(row.narrow(0, 0, nnz), col.narrow(0, 0, nnz));
+  }
+  DGS_CHECK_RC(dgs_sample_plan(&indptr, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), w.sizes,
+                               w.status, stream));
+  sync_stream();
+  nnz = w.sizes[0];
+  check_status("sample_neighbors");
+  row = torch::empty({nnz}, opt);
+  col = torch::empty({nnz}, opt);
+  run(row, col, nnz, nullptr);
+  return std::make_tuple(row, col);
+}
+
+}  // namespace
+
+std::tuple<torch::Tensor, torch::Tensor> RowWiseSamplingUniformCUDA(torch::Tensor seeds, torch::Tensor indptr,
+                                                                    torch::Tensor indices,
+                                                                    int64_t num_picks, bool replace) {
+  CHECK_CUDA(indptr);
+  CHECK_CUDA(indices);
+  indptr = indptr.contiguous();
+  indices = indices.contiguous();
+  return sample_impl(seeds, plain_desc(indptr), indptr.scalar_type(), plain_desc(indices),
+                     indices.scalar_type(), nullptr, num_picks, replace);
+}
+
+std::tuple<torch::Tensor, torch::Tensor> RowWiseSamplingUniformWithChunkTensorCUDA(
+    torch::Tensor seeds, c10::intrusive_ptr<ChunkTensor> indptr, c10::intrusive_ptr<ChunkTensor> indices,
+    int64_t num_picks, bool replace) {
+  return sample_impl(seeds, indptr->desc(), indptr->dtype(), indices->desc(), indices->dtype(), nullptr,
+                     num_picks, replace);
+}
+
+std::tuple<torch::Tensor, torch::Tensor> RowWiseSamplingProbCUDA(torch::Tensor seeds, torch::Tensor indptr,
+                                                                 torch::Tensor indices, torch::Tensor probs,
+                                                                 int64_t num_picks, bool replace) {
+  CHECK_CUDA(indptr);
+  CHECK_CUDA(indices);
+  CHECK_CUDA(probs);
+  TORCH_CHECK(probs.scalar_type() == torch::kFloat, "probs must be float32");
+  indptr = indptr.contiguous();
+  indices = indices.contiguous();
+  probs = probs.contiguous();
+  const dgs_chunk_desc pd = plain_desc(probs);
+  return sample_impl(seeds, plain_desc(indptr), indptr.scalar_type(), plain_desc(indices),
+                     indices.scalar_type(), &pd, num_picks, replace);
+}
+
+std::tuple<torch::Tensor, torch::Tensor> RowWiseSamplingProbWithChunkTensorCUDA(
+    torch::Tensor seeds, c10::intrusive_ptr<ChunkTensor> indptr, c10::intrusive_ptr<ChunkTensor> indices,
+    c10::intrusive_ptr<ChunkTensor> probs, int64_t num_picks, bool replace) {
+  TORCH_CHECK(probs->dtype() == torch::kFloat, "probs must be float32");
+  return sample_impl(seeds, indptr->desc(), indptr->dtype(), indices->desc(), indices->dtype(),
+                     &probs->desc(), num_picks, replace);
+}
+
+// ===========================================================================
+// relabel
+// ===========================================================================
+namespace {
+// Up to DGS_MAX_SEGMENTS tensors are passed as a segment list; longer lists
+// are concatenated first.  `keep` holds the contiguous tensors alive.
+dgs_segments make_segments(const std::vector<torch::Tensor>& ts, std::vector<torch::Tensor>& keep) {
+  dgs_segments s;
+  std::memset(&s, 0, sizeof(s));
+  if (ts.size() > DGS_MAX_SEGMENTS) {
+    keep.push_back(torch::cat(ts, 0).contiguous());
+    s.count = 1;
+    s.ptr[0] = keep.back().data_ptr();
+    s.len[0] = keep.back().numel();
+    return s;
+  }
+  s.count = static_cast<int32_t>(ts.size());
+  for (size_t i = 0; i < ts.size(); ++i) {
+    keep.push_back(ts[i].contiguous());
+    s.ptr[i] = keep.back().numel() ? keep.back().data_ptr() : nullptr;
+    s.len[i] = keep.back().numel();
+  }
+  return s;
+}
+}  // namespace
+
+std::tuple<torch::Tensor, std::vector<torch::Tensor>> TensorRelabelCUDA(
+    std::vector<torch::Tensor> mapping_tensors, std::vector<torch::Tensor> requiring_relabel_tensors) {
+  TORCH_CHECK(!mapping_tensors.empty(), "_CAPI_tensor_relabel: no mapping tensors");
+  check_status("_CAPI_tensor_relabel");
+  const torch::Tensor& first = mapping_tensors[0];
+  CHECK_CUDA(first);
+  const bool ids64 = is_id64(first, "mapping tensors");
+  for (const auto& t : mapping_tensors)
+    TORCH_CHECK(t.device() == first.device() && t.scalar_type() == first.scalar_type(),
+                "_CAPI_tensor_relabel: all tensors must share device and id type");
+  for (const auto& t : requiring_relabel_tensors)
+    TORCH_CHECK(t.device() == first.device() && t.scalar_type() == first.scalar_type(),
+                "_CAPI_tensor_relabel: all tensors must share device and id type");
+  c10::cuda::CUDAGuard guard(first.device());
+  cudaStream_t stream = current_stream();
+  HostWords& w = host_words();
+
+  std::vector<torch::Tensor> keep;
+  const dgs_segments keys = make_segments(mapping_tensors, keep);
+  int64_t n_keys = 0;
+  for (int i = 0; i < keys.count; ++i) n_keys += keys.len[i];
+  const dgs_segments req = make_segments(requiring_relabel_tensors, keep);
+  int64_t n_req = 0;
+  std::vector<int64_t> split_sizes;
+  for (const auto& t : requiring_relabel_tensors) {
+    split_sizes.push_back(t.numel());
+    n_req += t.numel();
+  }
+
+  const size_t tb = dgs_relabel_table_bytes(n_keys);
+  torch::Tensor table = byte_scratch(tb, first.device());
+  torch::Tensor uniq = torch::empty({n_keys}, first.options());
+  torch::Tensor out = torch::empty({n_req}, first.options());
+  DGS_CHECK_RC(dgs_unique_first_occurrence(&keys, ids64, table.data_ptr(), tb, uniq.data_ptr(), w.sizes,
+                                           w.status, stream));
+  DGS_CHECK_RC(dgs_relabel_lookup(table.data_ptr(), tb, n_keys, &req, ids64, out.data_ptr(), stream));
+  sync_stream();
+  const int64_t nu = w.sizes[0];
+  check_status("_CAPI_tensor_relabel");
+  TORCH_CHECK(nu >= 0 && nu <= n_keys, "dgs: relabel returned an impossible size");
+  return std::make_tuple(uniq.narrow(0, 0, nu), out.split_with_sizes(split_sizes, 0));
+}
+
+// ===========================================================================
+// PaGraph-style cache
+// ===========================================================================
+std::tuple<torch::Tensor, torch::Tensor> CreateHashMapTensorCUDA(torch::Tensor input_key,
+                                                                 torch::Tensor input_value) {
+  CHECK_CUDA(input_key);
+  CHECK_CUDA(input_value);
+  check_status("_CAPI_create_hash_map");
+  const bool ids64 = is_id64(input_key, "input_key");
+  TORCH_CHECK(input_value.scalar_type() == input_key.scalar_type(), "key and value must share one id type");
+  TORCH_CHECK(input_value.numel() == input_key.numel(), "key and value must have the same length");
+  c10::cuda::CUDAGuard guard(input_key.device());
+  input_key = input_key.contiguous();
+  input_value = input_value.contiguous();
+  const int64_t n = input_key.numel();
+  const int64_t slots = dgs_cache_table_slots(n);
+  torch::Tensor kb = torch::empty({slots}, input_key.options());
+  torch::Tensor vb = torch::empty({slots}, input_value.options());
+  DGS_CHECK_RC(dgs_cache_build(input_key.data_ptr(), input_value.data_ptr(), ids64, n, kb.data_ptr(),
+                               vb.data_ptr(), slots, host_words().status, current_stream()));
+  return std::make_tuple(kb, vb);
+}
+
+namespace {
+torch::Tensor fetch_impl(torch::Tensor cpu_data, const dgs_chunk_desc& gpu, torch::ScalarType gpu_dtype,
+                         torch::Tensor nid, torch::Tensor hk, torch::Tensor hv) {
+  CHECK_CUDA(nid);
+  CHECK_CUDA(hk);
+  CHECK_CUDA(hv);
+  check_status("_CAPI_fetch_data");
+  TORCH_CHECK(cpu_data.dim() == 2 && cpu_data.is_contiguous(), "cpu_data must be a contiguous 2-D tensor");
+  TORCH_CHECK(cpu_data.is_cuda() || cpu_data.is_pinned(),
+              "cpu_data must be pinned (page-locked) so that the GPU can read it in place");
+  TORCH_CHECK(cpu_data.scalar_type() == gpu_dtype, "cpu_data and gpu_data must share one dtype");
+  const bool ids64 = is_id64(nid, "nid");
+  TORCH_CHECK(hk.scalar_type() == nid.scalar_type() && hv.scalar_type() == nid.scalar_type(),
+              "nid and the hash tensors must share one id type");
+  c10::cuda::CUDAGuard guard(nid.device());
+  nid = nid.contiguous();
+  const int64_t n = nid.numel(), D = cpu_data.size(1);
+  torch::Tensor out = torch::empty({n, D}, torch::TensorOptions().dtype(gpu_dtype).device(nid.device()));
+  DGS_CHECK_RC(dgs_cache_fetch(cpu_data.data_ptr(), cpu_data.size(0), &gpu, nid.data_ptr(), ids64, n, D,
+                               hk.data_ptr(), hv.data_ptr(), hk.numel(), out.data_ptr(), host_words().status,
+                               current_stream()));
+  return out;
+}
+}  // namespace
+
+torch::Tensor FetchDataCUDA(torch::Tensor cpu_data, torch::Tensor gpu_data, torch::Tensor nid,
+                            torch::Tensor hashed_key_tensor, torch::Tensor hashed_value_tensor) {
+  CHECK_CUDA(gpu_data);
+  gpu_data = gpu_data.contiguous();
+  return fetch_impl(cpu_data, plain_desc(gpu_data), gpu_data.scalar_type(), nid, hashed_key_tensor,
+                    hashed_value_tensor);
+}
+
+torch::Tensor FetchDataWithChunkTensorCUDA(torch::Tensor cpu_data, c10::intrusive_ptr<ChunkTensor> gpu_data,
+                                           torch::Tensor nid, torch::Tensor hashed_key_tensor,
+                                           torch::Tensor hashed_value_tensor) {
+  return fetch_impl(cpu_data, gpu_data->desc(), gpu_data->dtype(), nid, hashed_key_tensor,
+                    hashed_value_tensor);
+}
+
+// ===========================================================================
+// communicator + bookkeeping
+// ===========================================================================
+std::vector<int64_t> GetUniqueId() {
+  std::vector<int64_t> id(16);
+  DGS_CHECK_RC(dgs_comm_get_unique_id(id.data()));
+  return id;
+}
+
+void SetNCCL(int64_t nranks, std::vector<int64_t> unique_id_array, int64_t rank) {
+  TORCH_CHECK(unique_id_array.size() >= 16, "_CAPI_set_nccl: unique id must hold 16 int64");
+  DGS_CHECK_RC(dgs_comm_init(nranks, unique_id_array.data(), rank));
+}
+
+int64_t GetCurrAllocated() { return dgs_alloc_current_bytes(); }
+
+}  // namespace dgs
+
+using namespace dgs;
+
+TORCH_LIBRARY(dgs_classes, m) {
+  m.class_<ChunkTensor>("ChunkTensor")
+      .def(torch::init<std::vector<int64_t>, torch::ScalarType, int64_t>())
+      .def("_CAPI_get_host_tensor", &ChunkTensor::GetHostTensor)
+      .def("_CAPI_get_sub_device_tensor", &ChunkTensor::GetSubDeviceTensor)
+      .def("_CAPI_index", &ChunkTensor::Index)
+      .def("_CAPI_split_index", &ChunkTensor::SplitIndex)
+      .def("_CAPI_local_index", &ChunkTensor::LocalIndex)
+      .def("_CAPI_remote_index", &ChunkTensor::RemoteIndex)
+      .def("_CAPI_host_index", &ChunkTensor::HostIndex)
+      .def("_CAPI_load_from_tensor", &ChunkTensor::LoadFromTensor);
+}
+
+TORCH_LIBRARY(dgs_ops, m) {
+  m.def("_CAPI_tensor_relabel", &TensorRelabelCUDA)
+      .def("_CAPI_sample_neighbors", &RowWiseSamplingUniformCUDA)
+      .def("_CAPI_sample_neighbors_with_chunk_tensor", &RowWiseSamplingUniformWithChunkTensorCUDA)
+      .def("_CAPI_sample_neighbors_with_probs", &RowWiseSamplingProbCUDA)
+      .def("_CAPI_sample_neighbors_with_probs_with_chunk_tensor", &RowWiseSamplingProbWithChunkTensorCUDA)
+      .def("_CAPI_create_hash_map", &CreateHashMapTensorCUDA)
+      .def("_CAPI_fetch_data", &FetchDataCUDA)
+      .def("_CAPI_fetch_data_chunk_tensor", &FetchDataWithChunkTensorCUDA)
+      .def("_CAPI_get_unique_id", &GetUniqueId)
+      .def("_CAPI_set_nccl", &SetNCCL)
+      .def("_CAPI_get_current_allocated", &GetCurrAllocated);
+}

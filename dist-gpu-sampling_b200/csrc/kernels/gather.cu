@@ -1,0 +1,424 @@
+// Row gather over a ChunkTensor:  out[i, :] = T[idx[i], :]
+//
+// Replaces _IndexMemcpyKernel / _Local.. / _Remote.. / _HostIndexMemcpyKernel
+// (reference src/cuda/index_with_chunk_tensor.cu:9-27,110-168), which run one
+// 128-thread block per row with scalar 4/8-byte accesses and re-resolve the
+// owner (three dependent metadata loads + a 64-bit divide) for every element.
+//
+// Design (HBM-bound copy, no tensor cores):
+//   * a CTA owns a tile of R consecutive output rows.  Phase 1 resolves each
+//     row ONCE (owner chunk / host tail, bounds, straddle) and parks the source
+//     pointer in shared memory.  Phase 2 treats the tile as R*nvec vectors of
+//     VEC bytes: consecutive threads move consecutive 16-byte pieces, so every
+//     lane is busy whatever the row width (D = 100 fp32 -> 25 vectors/row) and
+//     the output side is one contiguous, fully coalesced stream.  Eight
+//     independent vector loads are in flight per thread before the first store.
+//   * VEC (16/8/4/2/1 bytes) is picked on the host as the largest power of two
+//     dividing the row size and every base offset, so all rows that lie inside
+//     one storage region take the vector path.  Rows that straddle a chunk
+//     boundary (at most one per boundary in the whole tensor) and out-of-range
+//     ids take a per-element path; out-of-range rows are zero-filled and
+//     reported through the status word instead of faulting.
+//   * peer chunks (cudaIpc-mapped, NVLink) and the host tail (pinned, UVA) are
+//     ordinary global addresses, read with the same ld.global.nc vector loads.
+#include "common.cuh"
+
+namespace dgs {
+namespace {
+
+constexpr int GATHER_BLOCK = 256;
+constexpr int GATHER_UNROLL = 8;
+constexpr int GATHER_MAX_ROWS = 1024;  // rows per tile upper bound (smem: 8 KB)
+
+template <int VEC> struct VecT;
+template <> struct VecT<16> { using type = uint4; };
+template <> struct VecT<8> { using type = uint2; };
+template <> struct VecT<4> { using type = uint32_t; };
+template <> struct VecT<2> { using type = uint16_t; };
+template <> struct VecT<1> { using type = uint8_t; };
+
+// tags stored in the shared pointer table
+#define DGS_ROW_ZERO reinterpret_cast<const char*>(uintptr_t(0))
+#define DGS_ROW_SLOW reinterpret_cast<const char*>(uintptr_t(1))
+
+// ---- row sources ------------------------------------------------------------
+// A row source maps output row i to the address of its D elements, or to one
+// of the two tags above.  `slow_row` copies a tagged-slow row element-wise.
+
+// rows of a ChunkTensor selected by idx[i]
+template <typename IdxT>
+struct ChunkRows {
+  dgs_chunk_desc d;
+  const IdxT* idx;
+  int64_t D;
+  int64_t n_rows_total;  // rows lying fully inside the tensor
+  int sh;
+
+  __device__ __forceinline__ const char* locate(int64_t i, int vec, int32_t* status) const {
+    const int64_t row = static_cast<int64_t>(idx[i]);
+    if (row < 0 || row >= n_rows_total) {
+      raise_status(status, DGS_ERR_RANGE);
+      return DGS_ROW_ZERO;
+    }
+    int64_t run;
+    const char* src = resolve(d, sh, row * D, &run);
+    if (run < D || (reinterpret_cast<uintptr_t>(src) & (vec - 1)) != 0) return DGS_ROW_SLOW;
+    return src;
+  }
+  __device__ __forceinline__ const char* element(int64_t i, int64_t j) const {
+    int64_t run;
+    return resolve(d, sh, static_cast<int64_t>(idx[i]) * D + j, &run);
+  }
+};
+
+// PaGraph-style cached rows: nid[i] is looked up in an open-addressing table
+// (keys/values); a hit reads row `value` of the GPU-side ChunkTensor, a miss
+// reads row nid[i] of the device-visible host array.
+// Replaces _FetchDataKernel / _FetchDataWithChunkTensorKernel
+// (reference src/cuda/pagraph.cu:126-194).
+__device__ __forceinline__ uint64_t cache_hash(long long key) {
+  uint64_t z = static_cast<uint64_t>(key);
+  z = (z ^ (z >> 33)) * 0xFF51AFD7ED558CCDull;
+  z = (z ^ (z >> 33)) * 0xC4CEB9FE1A85EC53ull;
+  return z ^ (z >> 33);
+}
+
+template <typename IdxT>
+struct CachedRows {
+  dgs_chunk_desc gpu;
+  const char* cpu_data;
+  const IdxT* nid;
+  const IdxT* keys;
+  const IdxT* values;
+  uint64_t mask;  // slots - 1
+  int64_t D;
+  int64_t gpu_rows;
+  int64_t cpu_rows;
+  int sh;
+
+  __device__ __forceinline__ int64_t cached_row(int64_t id) const {
+    uint64_t h = cache_hash(id) & mask;
+    for (uint64_t probes = 0; probes <= mask; ++probes) {
+      const long long k = static_cast<long long>(keys[h]);
+      if (k == id) return static_cast<int64_t>(values[h]);
+      if (k == -1) return -1;
+      h = (h + 1) & mask;
+    }
+    return -1;
+  }
+  __device__ __forceinline__ const char* locate(int64_t i, int vec, int32_t* status) const {
+    const int64_t id = static_cast<int64_t>(nid[i]);
+    if (id < 0) {
+      raise_status(status, DGS_ERR_RANGE);
+      return DGS_ROW_ZERO;
+    }
+    const int64_t row = cached_row(id);
+    if (row < 0 && id < cpu_rows) return cpu_data + (id * D << sh);  // miss: host row
+    if (row < 0 || row >= gpu_rows) {
+      raise_status(status, DGS_ERR_RANGE);
+      return DGS_ROW_ZERO;
+    }
+    int64_t run;
+    const char* src = resolve(gpu, sh, row * D, &run);
+    if (run < D || (reinterpret_cast<uintptr_t>(src) & (vec - 1)) != 0) return DGS_ROW_SLOW;
+    return src;
+  }
+  __device__ __forceinline__ const char* element(int64_t i, int64_t j) const {
+    int64_t run;  // only cached rows can be tagged slow
+    return resolve(gpu, sh, cached_row(static_cast<int64_t>(nid[i])) * D + j, &run);
+  }
+};
+
+template <typename Src, int VEC>
+__global__ void __launch_bounds__(GATHER_BLOCK)
+gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int64_t D, const int sh,
+                   const uint32_t nvec, const uint32_t rows_per_tile, const uint32_t div_magic,
+                   char* __restrict__ out, int32_t* __restrict__ status) {
+  using V = typename VecT<VEC>::type;
+  __shared__ const char* s_src[GATHER_MAX_ROWS];
+
+  const int64_t tile_row0 = static_cast<int64_t>(blockIdx.x) * rows_per_tile;
+  const uint32_t rows_here =
+      static_cast<uint32_t>(min(static_cast<int64_t>(rows_per_tile), n - tile_row0));
+
+  // ---- phase 1: one resolution per row -------------------------------------
+  bool any_special = false;
+  for (uint32_t r = threadIdx.x; r < rows_here; r += GATHER_BLOCK) {
+    const char* src = rows.locate(tile_row0 + r, VEC, status);
+    any_special |= (reinterpret_cast<uintptr_t>(src) <= 1);
+    s_src[r] = src;
+  }
+  const int block_special = __syncthreads_or(any_special ? 1 : 0);
+
+  // ---- phase 2: vector copy, contiguous on the output side -----------------
+  const uint32_t items = rows_here * nvec;
+  V* __restrict__ out_tile = reinterpret_cast<V*>(out + (tile_row0 * D << sh));
+  for (uint32_t q0 = 0; q0 < items; q0 += GATHER_BLOCK * GATHER_UNROLL) {
+    V v[GATHER_UNROLL];
+    bool ok[GATHER_UNROLL];
+#pragma unroll
+    for (int u = 0; u < GATHER_UNROLL; ++u) {
+      const uint32_t q = q0 + u * GATHER_BLOCK + threadIdx.x;
+      ok[u] = false;
+      if (q < items) {
+        // q / nvec, exact while q*nvec < 2^32 (div_magic = ceil(2^32 / nvec); 0: nvec == 1)
+        const uint32_t r = rows_per_tile == 1 ? 0u : (div_magic ? __umulhi(q, div_magic) : q);
+        const uint32_t j = q - r * nvec;
+        const char* src = s_src[r];
+        if (reinterpret_cast<uintptr_t>(src) > 1) {
+          ok[u] = true;
+          v[u] = ld_stream(reinterpret_cast<const V*>(src) + j);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < GATHER_UNROLL; ++u) {
+      const uint32_t q = q0 + u * GATHER_BLOCK + threadIdx.x;
+      if (ok[u]) out_tile[q] = v[u];
+    }
+  }
+
+  // ---- phase 3: rare rows (straddle a chunk boundary / out of range) -------
+  if (block_special) {
+    const int esz = 1 << sh;
+    for (uint32_t r = 0; r < rows_here; ++r) {
+      const char* src = s_src[r];
+      if (reinterpret_cast<uintptr_t>(src) > 1) continue;
+      char* dst = out + ((tile_row0 + r) * D << sh);
+      if (src == DGS_ROW_ZERO) {
+        for (int64_t b = threadIdx.x; b < (D << sh); b += GATHER_BLOCK) dst[b] = 0;
+      } else {
+        for (int64_t j = threadIdx.x; j < D; j += GATHER_BLOCK) {
+          const char* p = rows.element(tile_row0 + r, j);
+          char* q = dst + (j << sh);
+          switch (esz) {
+            case 8: *reinterpret_cast<uint64_t*>(q) = *reinterpret_cast<const uint64_t*>(p); break;
+            case 4: *reinterpret_cast<uint32_t*>(q) = *reinterpret_cast<const uint32_t*>(p); break;
+            case 2: *reinterpret_cast<uint16_t*>(q) = *reinterpret_cast<const uint16_t*>(p); break;
+            default: *q = *p; break;
+          }
+        }
+      }
+    }
+  }
+}
+
+template <typename Src, int VEC>
+int launch_gather(const Src& rows, int64_t n, int64_t D, int sh, void* out, int32_t* status,
+                  cudaStream_t stream) {
+  const int64_t row_bytes = D << sh;
+  const int64_t nvec64 = row_bytes / VEC;
+  // the in-tile index q < rows*nvec must keep q*nvec < 2^32 for the magic divide
+  DGS_REQUIRE(nvec64 <= (1 << 24), DGS_ERR_UNSUPPORTED, "gather: rows of %lld bytes are not supported",
+              (long long)row_bytes);
+  const uint32_t nvec = static_cast<uint32_t>(nvec64);
+  uint32_t rows_per_tile = (GATHER_BLOCK * GATHER_UNROLL) / nvec;
+  if (rows_per_tile < 1) rows_per_tile = 1;
+  if (rows_per_tile > GATHER_MAX_ROWS) rows_per_tile = GATHER_MAX_ROWS;
+  // rows > 1 implies rows*nvec <= 2048 and nvec <= 1024, so q*nvec < 2^21 in the kernel
+  const uint32_t magic =
+      nvec == 1 ? 0u : static_cast<uint32_t>(((1ull << 32) + nvec - 1) / nvec);
+  const int64_t tiles = (n + rows_per_tile - 1) / rows_per_tile;
+  DGS_REQUIRE(tiles <= 0x7fffffffLL, DGS_ERR_UNSUPPORTED, "gather: too many rows (%lld)", (long long)n);
+  gather_rows_kernel<Src, VEC><<<static_cast<unsigned>(tiles), GATHER_BLOCK, 0, stream>>>(
+      rows, n, D, sh, nvec, rows_per_tile, magic, static_cast<char*>(out), status);
+  DGS_LAUNCH_CHECK();
+  return DGS_OK;
+}
+
+template <typename Src>
+int dispatch_vec(int vec, const Src& rows, int64_t n, int64_t D, int sh, void* out, int32_t* status,
+                 cudaStream_t stream) {
+  switch (vec) {
+    case 16: return launch_gather<Src, 16>(rows, n, D, sh, out, status, stream);
+    case 8: return launch_gather<Src, 8>(rows, n, D, sh, out, status, stream);
+    case 4: return launch_gather<Src, 4>(rows, n, D, sh, out, status, stream);
+    case 2: return launch_gather<Src, 2>(rows, n, D, sh, out, status, stream);
+    default: return launch_gather<Src, 1>(rows, n, D, sh, out, status, stream);
+  }
+}
+
+template <typename IdxT>
+int run_gather(int vec, const dgs_chunk_desc& d, const void* idx, int64_t n, int64_t D, int sh,
+               void* out, int32_t* status, cudaStream_t stream) {
+  ChunkRows<IdxT> rows{d, static_cast<const IdxT*>(idx), D, d.total / D, sh};
+  return dispatch_vec(vec, rows, n, D, sh, out, status, stream);
+}
+
+// ---- cache table build -------------------------------------------------------
+// Replaces CreateHashMapTensorCUDA's insert pass (reference src/cuda/pagraph.cu:94-124).
+template <typename IdT>
+__global__ void __launch_bounds__(256)
+cache_build_kernel(const IdT* __restrict__ keys, const IdT* __restrict__ values, const int64_t n,
+                   IdT* key_buf, IdT* value_buf, const uint64_t mask, int32_t* __restrict__ status) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= n) return;
+  const IdT key = keys[i];
+  if (key < 0) {
+    raise_status(status, DGS_ERR_RANGE);
+    return;
+  }
+  uint64_t h = cache_hash(static_cast<long long>(key)) & mask;
+  for (uint64_t probes = 0; probes <= mask; ++probes) {
+    IdT cur = *reinterpret_cast<volatile IdT*>(&key_buf[h]);
+    if (cur == static_cast<IdT>(-1)) {
+      if (sizeof(IdT) == 8)
+        cur = static_cast<IdT>(atomicCAS(reinterpret_cast<unsigned long long*>(&key_buf[h]),
+                                         ~0ull, static_cast<unsigned long long>(key)));
+      else
+        cur = static_cast<IdT>(atomicCAS(reinterpret_cast<unsigned int*>(&key_buf[h]), ~0u,
+                                         static_cast<unsigned int>(key)));
+    }
+    if (cur == static_cast<IdT>(-1) || cur == key) {
+      value_buf[h] = values[i];  // duplicates: last writer wins, as in the reference (:27)
+      return;
+    }
+    h = (h + 1) & mask;
+  }
+  raise_status(status, DGS_ERR_TABLE_FULL);
+}
+
+template <typename IdxT>
+int run_cache_fetch(int vec, const dgs_chunk_desc& gpu, const void* cpu_data, int64_t cpu_rows,
+                    const void* nid,
+                    const void* keys, const void* values, int64_t slots, int64_t n, int64_t D,
+                    int sh, void* out, int32_t* status, cudaStream_t stream) {
+  CachedRows<IdxT> rows{gpu,
+                        static_cast<const char*>(cpu_data),
+                        static_cast<const IdxT*>(nid),
+                        static_cast<const IdxT*>(keys),
+                        static_cast<const IdxT*>(values),
+                        static_cast<uint64_t>(slots - 1),
+                        D,
+                        gpu.total / D,
+                        cpu_rows,
+                        sh};
+  return dispatch_vec(vec, rows, n, D, sh, out, status, stream);
+}
+
+// largest power of two <= 16 dividing x (x == 0 counts as "any")
+inline int pow2_div(uint64_t x) {
+  int v = 16;
+  while (v > 1 && (x % static_cast<uint64_t>(v)) != 0) v >>= 1;
+  return v;
+}
+
+}  // namespace
+
+int validate_desc(const dgs_chunk_desc* t, const char* who) {
+  DGS_REQUIRE(t != nullptr, DGS_ERR_INVALID, "%s: null descriptor", who);
+  DGS_REQUIRE(esz_log2(t->esz) >= 0, DGS_ERR_UNSUPPORTED, "%s: element size %d", who, t->esz);
+  DGS_REQUIRE(t->num_parts >= 1 && t->num_parts <= DGS_MAX_PARTS, DGS_ERR_INVALID,
+              "%s: num_parts %d outside 1..%d", who, t->num_parts, DGS_MAX_PARTS);
+  DGS_REQUIRE(t->total >= 0 && t->threshold >= 0 && t->threshold <= t->total && t->each >= 0,
+              DGS_ERR_INVALID, "%s: inconsistent sizes", who);
+  DGS_REQUIRE(t->threshold <= t->each * t->num_parts, DGS_ERR_INVALID,
+              "%s: threshold exceeds each*num_parts", who);
+  DGS_REQUIRE(t->threshold == t->total || t->host != nullptr, DGS_ERR_INVALID,
+              "%s: host tail missing", who);
+  if (t->threshold > 0)
+    for (int p = 0; p * t->each < t->threshold; ++p)
+      DGS_REQUIRE(t->dev[p] != nullptr, DGS_ERR_INVALID, "%s: chunk %d has no pointer", who, p);
+  return DGS_OK;
+}
+
+// Vector width usable for every row that lies inside one storage region.
+int gather_vec_bytes(const dgs_chunk_desc& d, int64_t D, const void* out) {
+  const int sh = esz_log2(d.esz);
+  uint64_t g = static_cast<uint64_t>(D) << sh;  // row bytes
+  int v = pow2_div(g);
+  v = min(v, pow2_div(reinterpret_cast<uintptr_t>(out)));
+  if (d.threshold > 0) {
+    for (int p = 0; p * d.each < d.threshold; ++p)
+      v = min(v, pow2_div(reinterpret_cast<uintptr_t>(d.dev[p])));
+    if (d.threshold > d.each) v = min(v, pow2_div(static_cast<uint64_t>(d.each) << sh));
+  }
+  if (d.threshold < d.total) {
+    v = min(v, pow2_div(reinterpret_cast<uintptr_t>(d.host)));
+    v = min(v, pow2_div(static_cast<uint64_t>(d.threshold) << sh));
+  }
+  return v;
+}
+
+}  // namespace dgs
+
+extern "C" int dgs_gather_rows(const dgs_chunk_desc* t, int32_t location_class, const void* idx,
+                               int32_t ids64, int64_t n, int64_t D, void* out, int32_t* status,
+                               dgs_stream_t stream) {
+  using namespace dgs;
+  (void)location_class;  // hint only: the owner is resolved per row for every class
+  int rc = validate_desc(t, "dgs_gather_rows");
+  if (rc != DGS_OK) return rc;
+  DGS_REQUIRE(n >= 0 && D >= 1, DGS_ERR_INVALID, "dgs_gather_rows: n=%lld D=%lld", (long long)n,
+              (long long)D);
+  if (n == 0) return DGS_OK;
+  DGS_REQUIRE(idx != nullptr && out != nullptr, DGS_ERR_INVALID, "dgs_gather_rows: null buffer");
+  const int sh = esz_log2(t->esz);
+  const int vec = gather_vec_bytes(*t, D, out);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return ids64 ? run_gather<int64_t>(vec, *t, idx, n, D, sh, out, status, s)
+               : run_gather<int32_t>(vec, *t, idx, n, D, sh, out, status, s);
+}
+
+extern "C" int64_t dgs_cache_table_slots(int64_t n_keys) {
+  // same growth rule as the reference (2 * next power of two above n, pagraph.cu:89-101)
+  int64_t p = 1;
+  while (p <= n_keys) p <<= 1;
+  return 2 * p;
+}
+
+extern "C" int dgs_cache_build(const void* keys, const void* values, int32_t ids64, int64_t n_keys,
+                               void* key_buf, void* value_buf, int64_t slots, int32_t* status,
+                               dgs_stream_t stream) {
+  using namespace dgs;
+  DGS_REQUIRE(n_keys >= 0 && slots >= 2 && (slots & (slots - 1)) == 0 && slots > n_keys, DGS_ERR_INVALID,
+              "dgs_cache_build: slots=%lld must be a power of two above n_keys=%lld", (long long)slots,
+              (long long)n_keys);
+  DGS_REQUIRE(key_buf != nullptr && value_buf != nullptr, DGS_ERR_INVALID, "dgs_cache_build: null table");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t esz = ids64 ? 8 : 4;
+  // empty key = -1; untouched values read as the id type's maximum like the reference's fill (:104-107)
+  DGS_CUDA_TRY(cudaMemsetAsync(key_buf, 0xFF, static_cast<size_t>(slots) * esz, s));
+  DGS_CUDA_TRY(cudaMemsetAsync(value_buf, 0x7F, static_cast<size_t>(slots) * esz, s));
+  if (n_keys == 0) return DGS_OK;
+  DGS_REQUIRE(keys != nullptr && values != nullptr, DGS_ERR_INVALID, "dgs_cache_build: null input");
+  const unsigned grid = static_cast<unsigned>((n_keys + 255) / 256);
+  if (ids64)
+    cache_build_kernel<int64_t><<<grid, 256, 0, s>>>(static_cast<const int64_t*>(keys),
+                                                     static_cast<const int64_t*>(values), n_keys,
+                                                     static_cast<int64_t*>(key_buf),
+                                                     static_cast<int64_t*>(value_buf),
+                                                     static_cast<uint64_t>(slots - 1), status);
+  else
+    cache_build_kernel<int32_t><<<grid, 256, 0, s>>>(static_cast<const int32_t*>(keys),
+                                                     static_cast<const int32_t*>(values), n_keys,
+                                                     static_cast<int32_t*>(key_buf),
+                                                     static_cast<int32_t*>(value_buf),
+                                                     static_cast<uint64_t>(slots - 1), status);
+  DGS_LAUNCH_CHECK();
+  return DGS_OK;
+}
+
+extern "C" int dgs_cache_fetch(const void* cpu_data, int64_t cpu_rows,
+                               const dgs_chunk_desc* gpu_data, const void* nid,
+                               int32_t ids64, int64_t n, int64_t D, const void* key_buf,
+                               const void* value_buf, int64_t slots, void* out, int32_t* status,
+                               dgs_stream_t stream) {
+  using namespace dgs;
+  int rc = validate_desc(gpu_data, "dgs_cache_fetch");
+  if (rc != DGS_OK) return rc;
+  DGS_REQUIRE(n >= 0 && D >= 1 && slots >= 2 && (slots & (slots - 1)) == 0, DGS_ERR_INVALID,
+              "dgs_cache_fetch: bad arguments");
+  if (n == 0) return DGS_OK;
+  DGS_REQUIRE(cpu_data != nullptr && nid != nullptr && key_buf != nullptr && value_buf != nullptr &&
+                  out != nullptr,
+              DGS_ERR_INVALID, "dgs_cache_fetch: null buffer");
+  const int sh = esz_log2(gpu_data->esz);
+  int vec = gather_vec_bytes(*gpu_data, D, out);
+  vec = min(vec, pow2_div(reinterpret_cast<uintptr_t>(cpu_data)));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return ids64 ? run_cache_fetch<int64_t>(vec, *gpu_data, cpu_data, cpu_rows, nid, key_buf, value_buf, slots, n, D,
+                                          sh, out, status, s)
+               : run_cache_fetch<int32_t>(vec, *gpu_data, cpu_data, cpu_rows, nid, key_buf, value_buf, slots, n, D,
+                                          sh, out, status, s);
+}

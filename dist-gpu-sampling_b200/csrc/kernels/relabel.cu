@@ -1,0 +1,299 @@
+// Unique (first-occurrence order) + relabel through an open-addressing table.
+//
+// Replaces RelabelHashmap / Unique / Relabel / TensorRelabelCUDA
+// (reference src/cuda/tensor_reindex.cu:11-205): three torch::full tables, two
+// torch::cat copies, four thrust passes that each re-probe the table, a cub
+// scan and a blocking read-back, with hash(key) = key & (cap-1) at a load
+// factor of up to 100 %.
+//
+// Kept (the contract): the i-th distinct key in first-occurrence order gets
+// label i; lookups return the label or -1.  The order is fixed by storing the
+// MINIMUM input index per key (atomicMin) exactly as the reference does
+// (:28,123), so the result does not depend on hash layout or thread timing.
+//
+// Different (the design):
+//   * one 16-byte slot {key, value} per entry (a probe touches one sector, not
+//     three arrays), mixed 64-bit hash, linear probing, load factor <= 50 %.
+//   * inputs are read through a segment list instead of being concatenated.
+//   * the insert pass remembers each input's slot, so later passes index the
+//     table directly instead of probing again.
+//   * numbering is count-per-tile -> scan of tile sums -> write; the label is
+//     stored into the slot's value with the top bit set, which can never be
+//     mistaken for an input index by a concurrent reader, so no third table.
+//   * the number of distinct keys goes to a caller-supplied (pinned) word.
+#include "common.cuh"
+#include "philox.cuh"
+#include "tile_scan.cuh"
+
+namespace dgs {
+namespace {
+
+constexpr int RL_BLOCK = 256;
+constexpr int RL_ITEMS = 4;
+constexpr int RL_TILE = RL_BLOCK * RL_ITEMS;
+constexpr unsigned long long LABEL_BIT = 0x8000000000000000ull;
+constexpr long long EMPTY_KEY = -1;  // memset 0xFF: key = -1, value = 2^64-1
+constexpr uint32_t NO_SLOT = 0xFFFFFFFFu;
+
+struct __align__(16) Slot {
+  long long key;
+  unsigned long long val;
+};
+
+struct TableView {
+  Slot* slots;         // [cap]
+  uint32_t* slot_of;   // [n]  slot of every input
+  int64_t* tile_off;   // [ntiles]
+  int64_t* total;      // [1]
+  uint64_t cap;
+  int64_t ntiles;
+};
+
+inline uint64_t table_capacity(int64_t n) {
+  uint64_t cap = 64;
+  while (cap < 2 * static_cast<uint64_t>(n)) cap <<= 1;
+  return cap;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+inline TableView table_view(void* mem, int64_t n) {
+  TableView t;
+  t.cap = table_capacity(n);
+  t.ntiles = (n + RL_TILE - 1) / RL_TILE;
+  char* p = static_cast<char*>(mem);
+  t.slots = reinterpret_cast<Slot*>(p);
+  p += t.cap * sizeof(Slot);
+  t.slot_of = reinterpret_cast<uint32_t*>(p);
+  p += align_up(static_cast<size_t>(n) * sizeof(uint32_t), 16);
+  t.tile_off = reinterpret_cast<int64_t*>(p);
+  t.total = t.tile_off + t.ntiles;
+  return t;
+}
+
+__device__ __forceinline__ uint64_t hash_key(long long key) {
+  uint64_t z = static_cast<uint64_t>(key);
+  z = (z ^ (z >> 33)) * 0xFF51AFD7ED558CCDull;
+  z = (z ^ (z >> 33)) * 0xC4CEB9FE1A85EC53ull;
+  return z ^ (z >> 33);
+}
+
+// pass 1: insert every key, keep the smallest input index per key
+template <typename IdT>
+__global__ void __launch_bounds__(RL_BLOCK)
+relabel_insert_kernel(const __grid_constant__ dgs_segments keys, const int64_t n, Slot* slots,
+                      const uint64_t mask, uint32_t* __restrict__ slot_of,
+                      int32_t* __restrict__ status) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
+  if (i >= n) return;
+  const long long key = static_cast<long long>(seg_load<IdT>(keys, i));
+  if (key < 0) {
+    raise_status(status, DGS_ERR_RANGE);
+    slot_of[i] = NO_SLOT;
+    return;
+  }
+  uint64_t h = hash_key(key) & mask;
+  uint32_t found = NO_SLOT;
+  for (uint64_t probes = 0; probes <= mask; ++probes) {
+    long long cur = *reinterpret_cast<volatile long long*>(&slots[h].key);
+    if (cur == EMPTY_KEY)
+      cur = static_cast<long long>(atomicCAS(reinterpret_cast<unsigned long long*>(&slots[h].key),
+                                             static_cast<unsigned long long>(EMPTY_KEY),
+                                             static_cast<unsigned long long>(key)));
+    if (cur == EMPTY_KEY || cur == key) {
+      found = static_cast<uint32_t>(h);
+      break;
+    }
+    h = (h + 1) & mask;
+  }
+  slot_of[i] = found;
+  if (found == NO_SLOT) {
+    raise_status(status, DGS_ERR_TABLE_FULL);
+    return;
+  }
+  // values only ever decrease, so a stale read can only cause a redundant atomic
+  if (*reinterpret_cast<volatile unsigned long long*>(&slots[found].val) > static_cast<unsigned long long>(i))
+    atomicMin(&slots[found].val, static_cast<unsigned long long>(i));
+}
+
+// pass 2: input i is a first occurrence iff the stored minimum equals i
+__global__ void __launch_bounds__(RL_BLOCK)
+relabel_count_kernel(const int64_t n, const Slot* __restrict__ slots,
+                     const uint32_t* __restrict__ slot_of, int64_t* __restrict__ tile_sums) {
+  __shared__ int s_cnt;
+  if (threadIdx.x == 0) s_cnt = 0;
+  __syncthreads();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * RL_TILE + threadIdx.x * RL_ITEMS;
+  int c = 0;
+#pragma unroll
+  for (int u = 0; u < RL_ITEMS; ++u) {
+    const int64_t i = base + u;
+    if (i < n) {
+      const uint32_t s = slot_of[i];
+      if (s != NO_SLOT && slots[s].val == static_cast<unsigned long long>(i)) ++c;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(FULL_MASK, c, o);
+  if ((threadIdx.x & 31) == 0 && c) atomicAdd(&s_cnt, c);
+  __syncthreads();
+  if (threadIdx.x == 0) tile_sums[blockIdx.x] = s_cnt;
+}
+
+// pass 3: number the first occurrences, emit them, store the label in the slot
+template <typename IdT>
+__global__ void __launch_bounds__(RL_BLOCK)
+relabel_number_kernel(const __grid_constant__ dgs_segments keys, const int64_t n, Slot* slots,
+                      const uint32_t* __restrict__ slot_of, const int64_t* __restrict__ tile_off,
+                      IdT* __restrict__ unique_out) {
+  __shared__ int smem[RL_BLOCK / 32 + 1];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * RL_TILE + threadIdx.x * RL_ITEMS;
+  bool first[RL_ITEMS];
+  uint32_t slot[RL_ITEMS];
+  int c = 0;
+#pragma unroll
+  for (int u = 0; u < RL_ITEMS; ++u) {
+    const int64_t i = base + u;
+    first[u] = false;
+    slot[u] = NO_SLOT;
+    if (i < n) {
+      slot[u] = slot_of[i];
+      // a slot already relabelled by another CTA carries LABEL_BIT and cannot equal i
+      first[u] = slot[u] != NO_SLOT &&
+                 *reinterpret_cast<const volatile unsigned long long*>(&slots[slot[u]].val) ==
+                     static_cast<unsigned long long>(i);
+      c += first[u] ? 1 : 0;
+    }
+  }
+  int total;
+  const int ex = block_exclusive_scan<int, RL_BLOCK>(c, smem, &total);
+  int64_t label = tile_off[blockIdx.x] + ex;
+#pragma unroll
+  for (int u = 0; u < RL_ITEMS; ++u) {
+    if (first[u]) {
+      unique_out[label] = seg_load<IdT>(keys, base + u);
+      slots[slot[u]].val = LABEL_BIT | static_cast<unsigned long long>(label);
+      ++label;
+    }
+  }
+}
+
+// lookup: label of each id, -1 when absent
+template <typename IdT>
+__global__ void __launch_bounds__(RL_BLOCK)
+relabel_lookup_kernel(const __grid_constant__ dgs_segments in, const int64_t n,
+                      const Slot* __restrict__ slots, const uint64_t mask, IdT* __restrict__ out) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
+  if (i >= n) return;
+  const long long key = static_cast<long long>(seg_load<IdT>(in, i));
+  IdT res = static_cast<IdT>(-1);
+  if (key >= 0) {
+    uint64_t h = hash_key(key) & mask;
+    for (uint64_t probes = 0; probes <= mask; ++probes) {
+      const Slot s = slots[h];  // one 16-byte load
+      if (s.key == key) {
+        res = static_cast<IdT>(s.val & ~LABEL_BIT);
+        break;
+      }
+      if (s.key == EMPTY_KEY) break;
+      h = (h + 1) & mask;
+    }
+  }
+  out[i] = res;
+}
+
+inline int64_t seg_total(const dgs_segments& s) {
+  int64_t t = 0;
+  for (int i = 0; i < s.count; ++i) t += s.len[i];
+  return t;
+}
+
+int check_segments(const dgs_segments* s, const char* who) {
+  DGS_REQUIRE(s != nullptr && s->count >= 0 && s->count <= DGS_MAX_SEGMENTS, DGS_ERR_INVALID,
+              "%s: bad segment list", who);
+  for (int i = 0; i < s->count; ++i)
+    DGS_REQUIRE(s->len[i] >= 0 && (s->len[i] == 0 || s->ptr[i] != nullptr), DGS_ERR_INVALID,
+                "%s: segment %d is null", who, i);
+  return DGS_OK;
+}
+
+__global__ void zero_word_kernel(int64_t* w) { *w = 0; }
+
+template <typename IdT>
+int run_unique(const dgs_segments& keys, int64_t n, const TableView& t, void* unique_out,
+               int64_t* n_unique, int32_t* status, cudaStream_t s) {
+  DGS_CUDA_TRY(cudaMemsetAsync(t.slots, 0xFF, t.cap * sizeof(Slot), s));
+  const unsigned per_key_grid = static_cast<unsigned>((n + RL_BLOCK - 1) / RL_BLOCK);
+  relabel_insert_kernel<IdT><<<per_key_grid, RL_BLOCK, 0, s>>>(keys, n, t.slots, t.cap - 1, t.slot_of, status);
+  DGS_LAUNCH_CHECK();
+  relabel_count_kernel<<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(n, t.slots, t.slot_of, t.tile_off);
+  DGS_LAUNCH_CHECK();
+  tile_scan_kernel<1><<<1, TILE_SCAN_BLOCK, 0, s>>>(t.tile_off, t.ntiles, t.total, n_unique);
+  DGS_LAUNCH_CHECK();
+  relabel_number_kernel<IdT><<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(
+      keys, n, t.slots, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out));
+  DGS_LAUNCH_CHECK();
+  return DGS_OK;
+}
+
+}  // namespace
+}  // namespace dgs
+
+extern "C" size_t dgs_relabel_table_bytes(int64_t n) {
+  using namespace dgs;
+  if (n < 0) n = 0;
+  const int64_t ntiles = (n + RL_TILE - 1) / RL_TILE;
+  return table_capacity(n) * sizeof(Slot) + align_up(static_cast<size_t>(n) * sizeof(uint32_t), 16) +
+         static_cast<size_t>(ntiles + 1) * sizeof(int64_t);
+}
+
+extern "C" int dgs_unique_first_occurrence(const dgs_segments* keys, int32_t ids64, void* table,
+                                           size_t table_bytes, void* unique_out, int64_t* n_unique,
+                                           int32_t* status, dgs_stream_t stream) {
+  using namespace dgs;
+  int rc = check_segments(keys, "dgs_unique_first_occurrence");
+  if (rc != DGS_OK) return rc;
+  const int64_t n = seg_total(*keys);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  DGS_REQUIRE(table != nullptr && table_bytes >= dgs_relabel_table_bytes(n), DGS_ERR_INVALID,
+              "dgs_unique_first_occurrence: table scratch too small (%zu < %zu)", table_bytes,
+              dgs_relabel_table_bytes(n));
+  DGS_REQUIRE((reinterpret_cast<uintptr_t>(table) & 15) == 0, DGS_ERR_INVALID,
+              "dgs_unique_first_occurrence: table must be 16-byte aligned");
+  DGS_REQUIRE(n < (1ll << 30), DGS_ERR_UNSUPPORTED, "dgs_unique_first_occurrence: %lld keys", (long long)n);
+  const TableView t = table_view(table, n);
+  if (n == 0) {
+    DGS_CUDA_TRY(cudaMemsetAsync(t.slots, 0xFF, t.cap * sizeof(Slot), s));
+    if (n_unique != nullptr) {
+      zero_word_kernel<<<1, 1, 0, s>>>(n_unique);
+      DGS_LAUNCH_CHECK();
+    }
+    return DGS_OK;
+  }
+  DGS_REQUIRE(unique_out != nullptr, DGS_ERR_INVALID, "dgs_unique_first_occurrence: null output");
+  return ids64 ? run_unique<int64_t>(*keys, n, t, unique_out, n_unique, status, s)
+               : run_unique<int32_t>(*keys, n, t, unique_out, n_unique, status, s);
+}
+
+extern "C" int dgs_relabel_lookup(const void* table, size_t table_bytes, int64_t n_keys_built,
+                                  const dgs_segments* in, int32_t ids64, void* out,
+                                  dgs_stream_t stream) {
+  using namespace dgs;
+  int rc = check_segments(in, "dgs_relabel_lookup");
+  if (rc != DGS_OK) return rc;
+  const int64_t n = seg_total(*in);
+  if (n == 0) return DGS_OK;
+  DGS_REQUIRE(table != nullptr && n_keys_built >= 0 && table_bytes >= dgs_relabel_table_bytes(n_keys_built),
+              DGS_ERR_INVALID, "dgs_relabel_lookup: bad table");
+  DGS_REQUIRE(out != nullptr, DGS_ERR_INVALID, "dgs_relabel_lookup: null output");
+  DGS_REQUIRE((n + RL_BLOCK - 1) / RL_BLOCK <= 0x7fffffffLL, DGS_ERR_UNSUPPORTED, "dgs_relabel_lookup: too many ids");
+  const TableView t = table_view(const_cast<void*>(table), n_keys_built);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>((n + RL_BLOCK - 1) / RL_BLOCK);
+  if (ids64)
+    relabel_lookup_kernel<int64_t><<<grid, RL_BLOCK, 0, s>>>(*in, n, t.slots, t.cap - 1, static_cast<int64_t*>(out));
+  else
+    relabel_lookup_kernel<int32_t><<<grid, RL_BLOCK, 0, s>>>(*in, n, t.slots, t.cap - 1, static_cast<int32_t*>(out));
+  DGS_LAUNCH_CHECK();
+  return DGS_OK;
+}

@@ -1,0 +1,594 @@
+// Row-wise neighbour sampling on a CSC graph whose indptr / indices / weights
+// live in ChunkTensors (or plain device tensors: num_parts == 1).
+//
+// Replaces, for both the plain-tensor and the ChunkTensor operators:
+//   _GetSubIndptr + cub scan + blocking nnz read-back
+//       (reference src/cuda/rowwise_sampling.cu:13-40,147),
+//   _CSRRowWiseSampleUniformKernel / ...ReplaceKernel
+//       (src/cuda/rowwise_sampling.cu:42-136,
+//        src/cuda/rowwise_sampling_with_chunk_tensor.cu:15-111),
+//   _CSRRowWiseSampleKernel / ...ReplaceKernel (weighted)
+//       (src/cuda/rowwise_sampling_probs.cu:54-216) and the faiss-derived
+//       WarpSelect it uses (src/cuda/warpselect/*.cuh).
+//
+// What is kept (the contract): per-seed counts min(deg,k) / (deg?k:0); COO
+// grouped by seed position; rows with deg <= k copied whole in CSC order;
+// uniform k-subsets / A-Res weighted subsets / proportional draws otherwise.
+//
+// What is different (the design):
+//   * the reference spends one 128-thread block and one curand_init per seed
+//     and draws O(deg) random numbers per row (Algorithm R).  Here a seed gets
+//     a sub-warp group of G = 4..32 lanes (G >= k), the row is never scanned:
+//     k candidate positions are drawn at once with counter-based Philox and
+//     duplicates are re-drawn until the k positions are distinct
+//     (__match_any_sync across the warp).  Equal treatment of positions makes
+//     every k-subset equally likely.  When k > deg/2 the deg-k positions to
+//     LEAVE OUT are drawn instead, so a draw collides with probability < 1/2.
+//   * bounded integers use Lemire's multiply-shift with rejection instead of
+//     `rand % n`.
+//   * weighted sampling without replacement keeps the top-k keys in a sorted
+//     per-warp register list (lane i = i-th largest) with ballot-gated
+//     insertion; keys are compared in the log domain, log(u)/w, which orders
+//     exactly like u^(1/w) but does not underflow for small weights.
+//   * weighted sampling with replacement builds no cumulative array in global
+//     memory: the row is streamed twice through a warp scan and each draw is
+//     resolved by a ballot in the 32-edge window it falls into.
+//   * counts, offsets and the total are produced on the device; the total goes
+//     to a caller-supplied (pinned) word, so there is no mid-sequence stall.
+#include "common.cuh"
+#include "philox.cuh"
+#include "tile_scan.cuh"
+
+namespace dgs {
+namespace {
+
+constexpr int SAMPLE_TILE = 256;   // seeds per CTA
+constexpr int SAMPLE_BLOCK = 256;  // threads per CTA
+
+constexpr uint32_t TAG_UNIFORM = 0x554E4931u;
+constexpr uint32_t TAG_REPLACE = 0x5245504Cu;
+constexpr uint32_t TAG_FLOYD = 0x464C4F59u;
+constexpr uint32_t TAG_ARES = 0x41524553u;
+constexpr uint32_t TAG_WREPL = 0x57524550u;
+
+struct PlanView {
+  int64_t* row_begin;  // [n]
+  int64_t* deg;        // [n]
+  int64_t* tile_off;   // [ntiles]  per-tile sums, scanned in place
+  int64_t* total;      // [1]
+  int64_t ntiles;
+};
+
+inline PlanView plan_view(void* plan, int64_t n) {
+  PlanView v;
+  v.ntiles = (n + SAMPLE_TILE - 1) / SAMPLE_TILE;
+  v.row_begin = static_cast<int64_t*>(plan);
+  v.deg = v.row_begin + n;
+  v.tile_off = v.deg + n;
+  v.total = v.tile_off + v.ntiles;
+  return v;
+}
+
+__device__ __forceinline__ int64_t pick_count(int64_t deg, int64_t k, bool replace) {
+  return replace ? (deg > 0 ? k : 0) : (deg < k ? deg : k);
+}
+
+// ---------------------------------------------------------------------------
+// plan: row range per seed + per-tile output counts
+// ---------------------------------------------------------------------------
+template <typename IdT>
+__global__ void __launch_bounds__(SAMPLE_BLOCK)
+sample_plan_kernel(const __grid_constant__ dgs_chunk_desc indptr, const IdT* __restrict__ seeds,
+                   const int64_t n, const int64_t k, const bool replace,
+                   int64_t* __restrict__ row_begin, int64_t* __restrict__ deg_out,
+                   int64_t* __restrict__ tile_sums, int32_t* __restrict__ status) {
+  __shared__ int64_t smem[SAMPLE_BLOCK / 32 + 1];
+  constexpr int sh = sizeof(IdT) == 8 ? 3 : 2;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + threadIdx.x;
+  int64_t cnt = 0;
+  if (i < n) {
+    const int64_t s = static_cast<int64_t>(seeds[i]);
+    int64_t rb = 0, deg = 0;
+    if (s < 0 || s + 1 >= indptr.total) {
+      raise_status(status, DGS_ERR_RANGE);
+    } else {
+      int64_t run;
+      const IdT* p = reinterpret_cast<const IdT*>(resolve(indptr, sh, s, &run));
+      rb = static_cast<int64_t>(p[0]);
+      const int64_t re = run >= 2 ? static_cast<int64_t>(p[1]) : static_cast<int64_t>(load_at<IdT>(indptr, sh, s + 1));
+      deg = re - rb;
+      if (deg < 0 || rb < 0) {
+        raise_status(status, DGS_ERR_RANGE);
+        deg = 0;
+        rb = 0;
+      }
+    }
+    row_begin[i] = rb;
+    deg_out[i] = deg;
+    cnt = pick_count(deg, k, replace);
+  }
+  int64_t total;
+  block_exclusive_scan<int64_t, SAMPLE_BLOCK>(cnt, smem, &total);
+  if (threadIdx.x == 0) tile_sums[blockIdx.x] = total;
+}
+
+// ---------------------------------------------------------------------------
+// shared pieces of the sampling kernels
+// ---------------------------------------------------------------------------
+template <typename IdT>
+struct Emit {
+  const dgs_chunk_desc& indices;
+  IdT* coo_row;
+  IdT* coo_col;
+  int64_t* picked_pos;
+  int64_t out_capacity;
+  int32_t* status;
+
+  // t-th output of a seed whose outputs start at o; `pos` = position in its row
+  __device__ __forceinline__ void operator()(int64_t o, int64_t t, int64_t seed, int64_t rb,
+                                             int64_t pos) const {
+    constexpr int sh = sizeof(IdT) == 8 ? 3 : 2;
+    const int64_t at = o + t;
+    if (at >= out_capacity) {
+      raise_status(status, DGS_ERR_RANGE);
+      return;
+    }
+    const int64_t e = rb + pos;
+    IdT c = static_cast<IdT>(-1);
+    if (e >= 0 && e < indices.total) c = load_at<IdT>(indices, sh, e);
+    else raise_status(status, DGS_ERR_RANGE);
+    coo_row[at] = static_cast<IdT>(seed);
+    coo_col[at] = c;
+    if (picked_pos != nullptr) picked_pos[at] = pos;
+  }
+};
+
+// Phase A of both sampling kernels: per-seed output offsets of this tile.
+__device__ __forceinline__ void tile_offsets(const int64_t* __restrict__ plan_rb,
+                                             const int64_t* __restrict__ plan_deg,
+                                             const int64_t* __restrict__ tile_off, int64_t n,
+                                             int64_t k, bool replace, int64_t* s_off, int64_t* s_rb,
+                                             int64_t* s_deg, int64_t* s_scan) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + threadIdx.x;
+  int64_t deg = 0, rb = 0;
+  if (i < n) {
+    deg = plan_deg[i];
+    rb = plan_rb[i];
+  }
+  int64_t total;
+  const int64_t ex =
+      block_exclusive_scan<int64_t, SAMPLE_BLOCK>(pick_count(deg, k, replace), s_scan, &total);
+  s_off[threadIdx.x] = tile_off[blockIdx.x] + ex;
+  s_rb[threadIdx.x] = rb;
+  s_deg[threadIdx.x] = deg;
+  __syncthreads();
+}
+
+// ---------------------------------------------------------------------------
+// uniform sampling: G lanes per seed
+// ---------------------------------------------------------------------------
+template <typename IdT, int G>
+__global__ void __launch_bounds__(SAMPLE_BLOCK)
+sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT* __restrict__ seeds,
+                      const int64_t n, const int64_t k, const bool replace,
+                      const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
+                      const int64_t* __restrict__ tile_off, const uint64_t key,
+                      IdT* coo_row, IdT* coo_col, const int64_t out_capacity,
+                      int64_t* __restrict__ picked_pos, int32_t* __restrict__ status) {
+  __shared__ int64_t s_off[SAMPLE_TILE], s_rb[SAMPLE_TILE], s_deg[SAMPLE_TILE];
+  __shared__ int64_t s_scan[SAMPLE_BLOCK / 32 + 1];
+  tile_offsets(plan_rb, plan_deg, tile_off, n, k, replace, s_off, s_rb, s_deg, s_scan);
+
+  const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
+  constexpr int GROUPS = SAMPLE_BLOCK / G;
+  const int lane = threadIdx.x & 31;
+  const int l = threadIdx.x % G;        // lane inside the group
+  const int group = threadIdx.x / G;    // group inside the CTA
+  const int gw = lane / G;              // group inside the warp
+  const unsigned gmask = (G == 32) ? FULL_MASK : (((1u << G) - 1u) << (gw * G));
+  const bool fast = !replace && k <= G;  // uniform over the grid
+
+  for (int sl = group; sl < SAMPLE_TILE; sl += GROUPS) {  // same trip count for every group
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + sl;
+    const bool valid = i < n;
+    const int64_t deg = s_deg[sl], rb = s_rb[sl], o = s_off[sl];
+    const int64_t seed = valid ? static_cast<int64_t>(seeds[i]) : 0;
+    const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
+
+    if (replace) {
+      if (valid && deg > 0)
+        for (int64_t t = l; t < k; t += G) {
+          const Philox4 r = philox4x32_10(key, i_lo, i_hi, static_cast<uint32_t>(t), TAG_REPLACE);
+          emit(o, t, seed, rb, static_cast<int64_t>(bounded(r, static_cast<uint64_t>(deg))));
+        }
+      continue;
+    }
+
+    if (fast) {
+      // -- distinct positions by parallel rejection (all 32 lanes take part) --
+      const bool sampled = valid && deg > k;
+      const bool complement = sampled && 2 * k > deg;  // draw the deg-k positions to leave out
+      const int64_t m = sampled ? (complement ? deg - k : k) : 0;
+      const bool active = l < m;
+      bool need = active;
+      int64_t c = 0;
+      uint32_t round = 0;
+      while (__any_sync(FULL_MASK, need)) {
+        if (need) {
+          if (round < 64) {
+            const Philox4 r = philox4x32_10(key, i_lo, i_hi, (round << 8) | static_cast<uint32_t>(l), TAG_UNIFORM);
+            c = static_cast<int64_t>(bounded(r, static_cast<uint64_t>(deg)));
+          } else {  // never reached in practice: step to a free neighbour, keeps the loop bounded
+            c = (c + 1 == deg) ? 0 : c + 1;
+          }
+        }
+        const unsigned long long tag =
+            active ? (static_cast<unsigned long long>(c) | (static_cast<unsigned long long>(gw) << 58))
+                   : (0x8000000000000000ull | static_cast<unsigned long long>(lane));
+        const unsigned same = __match_any_sync(FULL_MASK, tag);
+        need = active && (__ffs(same) - 1 != lane);
+        if (++round >= 64 + 1024) {
+          if (need) raise_status(status, DGS_ERR_TABLE_FULL);
+          break;
+        }
+      }
+      if (__any_sync(FULL_MASK, complement)) {
+        // positions a = l and b = l + G cover the row (deg <= 2k <= 2G)
+        const int64_t a = l, b = l + G;
+        bool ex_a = false, ex_b = false;
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          const int64_t cj = __shfl_sync(FULL_MASK, c, j, G);
+          if (j < m) {
+            ex_a |= (cj == a);
+            ex_b |= (cj == b);
+          }
+        }
+        const bool in_a = complement && a < deg && !ex_a;
+        const bool in_b = complement && b < deg && !ex_b;
+        const unsigned ba = __ballot_sync(FULL_MASK, in_a) & gmask;
+        const unsigned bb = __ballot_sync(FULL_MASK, in_b) & gmask;
+        const unsigned lt = (1u << lane) - 1u;
+        if (in_a) emit(o, __popc(ba & lt), seed, rb, a);
+        if (in_b) emit(o, __popc(ba) + __popc(bb & lt), seed, rb, b);
+      }
+      if (sampled && !complement) {
+        if (active) emit(o, l, seed, rb, c);
+      } else if (valid && !sampled) {
+        if (l < deg) emit(o, l, seed, rb, l);  // whole row, CSC order (deg <= k <= G)
+      }
+      continue;
+    }
+
+    // -- general k (> G is only possible with G == 32: the group is the warp) --
+    if (!valid) continue;
+    if (deg <= k) {
+      for (int64_t t = l; t < deg; t += G) emit(o, t, seed, rb, t);
+    } else if (o + k > out_capacity) {
+      if (l == 0) raise_status(status, DGS_ERR_RANGE);
+    } else {
+      // Floyd's subset algorithm; the chosen positions are parked in coo_col
+      volatile IdT* slots = coo_col + o;
+      int64_t have = 0;
+      for (int64_t j = deg - k; j < deg; ++j, ++have) {
+        const Philox4 r = philox4x32_10(key, i_lo, i_hi, static_cast<uint32_t>(have), TAG_FLOYD);
+        const int64_t t = static_cast<int64_t>(bounded(r, static_cast<uint64_t>(j + 1)));
+        bool found = false;
+        for (int64_t q = l; q < have; q += G) found |= (static_cast<int64_t>(slots[q]) == t);
+        found = __any_sync(gmask, found);
+        if (l == 0) slots[have] = static_cast<IdT>(found ? j : t);
+        __syncwarp(gmask);
+      }
+      for (int64_t q = l; q < k; q += G) emit(o, q, seed, rb, static_cast<int64_t>(slots[q]));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// weighted sampling: one warp per seed
+// ---------------------------------------------------------------------------
+struct RowWeights {
+  const dgs_chunk_desc& probs;
+  const float* direct;  // non-null when the whole row lies in one storage region
+  int64_t rb;
+  __device__ __forceinline__ float operator()(int64_t e) const {
+    return direct != nullptr ? direct[e] : load_at<float>(probs, 2, rb + e);
+  }
+};
+
+template <typename IdT>
+__global__ void __launch_bounds__(SAMPLE_BLOCK)
+sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
+                       const __grid_constant__ dgs_chunk_desc probs, const IdT* __restrict__ seeds,
+                       const int64_t n, const int64_t k, const bool replace,
+                       const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
+                       const int64_t* __restrict__ tile_off, const uint64_t key, IdT* coo_row,
+                       IdT* coo_col, const int64_t out_capacity, int64_t* __restrict__ picked_pos,
+                       int32_t* __restrict__ status) {
+  __shared__ int64_t s_off[SAMPLE_TILE], s_rb[SAMPLE_TILE], s_deg[SAMPLE_TILE];
+  __shared__ int64_t s_scan[SAMPLE_BLOCK / 32 + 1];
+  tile_offsets(plan_rb, plan_deg, tile_off, n, k, replace, s_off, s_rb, s_deg, s_scan);
+
+  const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
+  const int l = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  constexpr int WARPS = SAMPLE_BLOCK / 32;
+  const float NEG_INF = __int_as_float(0xff800000);
+  const float FLOOR_ZERO_W = -3.402823466e+38f;  // weight <= 0: behind every positive weight
+  const float FLOOR_POS_W = -3.0e+38f;           // clamp for positive weights
+
+  for (int sl = warp; sl < SAMPLE_TILE; sl += WARPS) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + sl;
+    if (i >= n) break;  // warp-uniform
+    const int64_t deg = s_deg[sl], rb = s_rb[sl], o = s_off[sl];
+    const int64_t seed = static_cast<int64_t>(seeds[i]);
+    const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
+    if (deg <= 0) continue;
+
+    if (!replace && deg <= k) {
+      for (int64_t t = l; t < deg; t += 32) emit(o, t, seed, rb, t);
+      continue;
+    }
+    if (rb + deg > probs.total) {
+      if (l == 0) raise_status(status, DGS_ERR_RANGE);
+      continue;
+    }
+    int64_t run;
+    const char* wp = resolve(probs, 2, rb, &run);
+    const RowWeights W{probs, run >= deg ? reinterpret_cast<const float*>(wp) : nullptr, rb};
+
+    if (!replace) {
+      // ---- A-Res: keep the k largest log(u)/w; lane j holds the j-th largest ----
+      float top_key = NEG_INF;
+      int64_t top_pos = -1;
+      float thresh = NEG_INF;  // key held by lane k-1
+      for (int64_t base = 0; base < deg; base += 128) {
+        // one Philox block per lane covers the lane's four edges of this window
+        const uint64_t ctr = static_cast<uint64_t>(base >> 2) + static_cast<uint64_t>(l);
+        const Philox4 r = philox4x32_10(key ^ (static_cast<uint64_t>(TAG_ARES) << 32), i_lo, i_hi,
+                                        static_cast<uint32_t>(ctr), static_cast<uint32_t>(ctr >> 32));
+        const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+        float ck[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int64_t e = base + j * 32 + l;
+          ck[j] = NEG_INF;
+          if (e < deg) {
+            const float w = W(e);
+            ck[j] = (w > 0.f) ? fmaxf(__logf(unit_float(rw[j])) / w, FLOOR_POS_W) : FLOOR_ZERO_W;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          unsigned cand = __ballot_sync(FULL_MASK, ck[j] > thresh);
+          while (cand) {
+            const int src = __ffs(cand) - 1;
+            cand &= cand - 1;
+            const float nk = __shfl_sync(FULL_MASK, ck[j], src);
+            if (nk > thresh) {  // thresh may have risen since the ballot; uniform over the warp
+              const int64_t np = base + j * 32 + src;
+              const int p = __popc(__ballot_sync(FULL_MASK, top_key >= nk));  // p <= k-1
+              const float up_key = __shfl_up_sync(FULL_MASK, top_key, 1);
+              const int64_t up_pos = __shfl_up_sync(FULL_MASK, top_pos, 1);
+              if (l > p) {
+                top_key = up_key;
+                top_pos = up_pos;
+              } else if (l == p) {
+                top_key = nk;
+                top_pos = np;
+              }
+              thresh = __shfl_sync(FULL_MASK, top_key, static_cast<int>(k) - 1);
+            }
+          }
+        }
+      }
+      if (l < k) emit(o, l, seed, rb, top_pos);
+    } else {
+      // ---- proportional draws: stream the row twice through a warp scan ----
+      float total = 0.f;
+      for (int64_t base = 0; base < deg; base += 32) {
+        const int64_t e = base + l;
+        float w = (e < deg) ? fmaxf(W(e), 0.f) : 0.f;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const float t = __shfl_up_sync(FULL_MASK, w, d);
+          if (l >= d) w += t;
+        }
+        total = __shfl_sync(FULL_MASK, total + w, 31);
+      }
+      for (int64_t t0 = 0; t0 < k; t0 += 32) {
+        const int64_t t = t0 + l;
+        const bool mine = t < k;
+        const Philox4 r = philox4x32_10(key, i_lo, i_hi, static_cast<uint32_t>(t), TAG_WREPL);
+        const float draw = unit_float(r.x) * total;
+        bool done = !mine;
+        int64_t pos = deg - 1;  // a draw not below the final sum maps to the last edge
+        float carry = 0.f;
+        for (int64_t base = 0; base < deg; base += 32) {
+          const int64_t e = base + l;
+          float w = (e < deg) ? fmaxf(W(e), 0.f) : 0.f;
+#pragma unroll
+          for (int d = 1; d < 32; d <<= 1) {
+            const float x = __shfl_up_sync(FULL_MASK, w, d);
+            if (l >= d) w += x;
+          }
+          const float cdf = carry + w;  // inclusive prefix up to edge e
+          const float window_end = __shfl_sync(FULL_MASK, cdf, 31);
+          unsigned hit = __ballot_sync(FULL_MASK, !done && draw < window_end);
+          while (hit) {
+            const int src = __ffs(hit) - 1;
+            hit &= hit - 1;
+            const float d0 = __shfl_sync(FULL_MASK, draw, src);
+            const unsigned above = __ballot_sync(FULL_MASK, cdf > d0);  // non-empty: lane 31 is above
+            if (l == src) {
+              int64_t q = base + (__ffs(above) - 1);
+              pos = q < deg ? q : deg - 1;
+              done = true;
+            }
+          }
+          carry = window_end;
+          if (__all_sync(FULL_MASK, done)) break;
+        }
+        if (mine) emit(o, t, seed, rb, pos);
+      }
+    }
+  }
+}
+
+template <typename IdT>
+int launch_plan(const dgs_chunk_desc& indptr, const void* seeds, int64_t n, int64_t k, bool replace,
+                const PlanView& pv, int64_t* nnz, int32_t* status, cudaStream_t s) {
+  sample_plan_kernel<IdT><<<static_cast<unsigned>(pv.ntiles), SAMPLE_BLOCK, 0, s>>>(
+      indptr, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.tile_off, status);
+  DGS_LAUNCH_CHECK();
+  tile_scan_kernel<1><<<1, TILE_SCAN_BLOCK, 0, s>>>(pv.tile_off, pv.ntiles, pv.total, nnz);
+  DGS_LAUNCH_CHECK();
+  return DGS_OK;
+}
+
+__global__ void copy_total_kernel(const int64_t* total, int64_t* nnz) { *nnz = *total; }
+__global__ void zero_total_kernel(int64_t* nnz) { *nnz = 0; }
+
+template <typename IdT>
+int launch_uniform(const dgs_chunk_desc& indices, const void* seeds, int64_t n, int64_t k,
+                   bool replace, const PlanView& pv, uint64_t key, void* coo_row, void* coo_col,
+                   int64_t cap, int64_t* pos, int32_t* status, cudaStream_t s) {
+  const unsigned grid = static_cast<unsigned>(pv.ntiles);
+#define DGS_LAUNCH_U(G)                                                                          \
+  sample_uniform_kernel<IdT, G><<<grid, SAMPLE_BLOCK, 0, s>>>(                                   \
+      indices, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.tile_off, \
+      key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, status)
+  if (k <= 4) DGS_LAUNCH_U(4);
+  else if (k <= 8) DGS_LAUNCH_U(8);
+  else if (k <= 16) DGS_LAUNCH_U(16);
+  else DGS_LAUNCH_U(32);
+#undef DGS_LAUNCH_U
+  DGS_LAUNCH_CHECK();
+  return DGS_OK;
+}
+
+int check_sample_args(const char* who, const void* seeds, int64_t n, int64_t k, const void* plan) {
+  DGS_REQUIRE(n >= 0 && k >= 0, DGS_ERR_INVALID, "%s: n=%lld k=%lld", who, (long long)n, (long long)k);
+  DGS_REQUIRE(n == 0 || (seeds != nullptr && plan != nullptr), DGS_ERR_INVALID, "%s: null buffer", who);
+  DGS_REQUIRE((n + SAMPLE_TILE - 1) / SAMPLE_TILE <= 0x7fffffffLL, DGS_ERR_UNSUPPORTED,
+              "%s: too many seeds", who);
+  return DGS_OK;
+}
+
+}  // namespace
+}  // namespace dgs
+
+extern "C" size_t dgs_sample_plan_bytes(int64_t n) {
+  if (n < 0) n = 0;
+  const int64_t ntiles = (n + dgs::SAMPLE_TILE - 1) / dgs::SAMPLE_TILE;
+  return static_cast<size_t>(2 * n + ntiles + 1) * sizeof(int64_t);
+}
+
+extern "C" int dgs_sample_plan(const dgs_chunk_desc* indptr, const void* seeds, int32_t ids64,
+                               int64_t n, int64_t k, int32_t replace, void* plan, int64_t* nnz,
+                               int32_t* status, dgs_stream_t stream) {
+  using namespace dgs;
+  int rc = validate_desc(indptr, "dgs_sample_plan");
+  if (rc != DGS_OK) return rc;
+  rc = check_sample_args("dgs_sample_plan", seeds, n, k, plan);
+  if (rc != DGS_OK) return rc;
+  DGS_REQUIRE(indptr->esz == (ids64 ? 8 : 4), DGS_ERR_INVALID,
+              "dgs_sample_plan: indptr element size %d does not match the id type", indptr->esz);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n == 0) {
+    if (nnz != nullptr) {
+      zero_total_kernel<<<1, 1, 0, s>>>(nnz);
+      DGS_LAUNCH_CHECK();
+    }
+    return DGS_OK;
+  }
+  const PlanView pv = plan_view(plan, n);
+  return ids64 ? launch_plan<int64_t>(*indptr, seeds, n, k, replace != 0, pv, nnz, status, s)
+               : launch_plan<int32_t>(*indptr, seeds, n, k, replace != 0, pv, nnz, status, s);
+}
+
+extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* seeds, int32_t ids64,
+                                  int64_t n, int64_t k, int32_t replace, const void* plan,
+                                  uint64_t rng_seed, uint64_t rng_offset, void* coo_row,
+                                  void* coo_col, int64_t out_capacity, int64_t* nnz,
+                                  int64_t* picked_pos, int32_t* status, dgs_stream_t stream) {
+  using namespace dgs;
+  int rc = validate_desc(indices, "dgs_sample_uniform");
+  if (rc != DGS_OK) return rc;
+  rc = check_sample_args("dgs_sample_uniform", seeds, n, k, plan);
+  if (rc != DGS_OK) return rc;
+  DGS_REQUIRE(indices->esz == (ids64 ? 8 : 4), DGS_ERR_INVALID,
+              "dgs_sample_uniform: indices element size %d does not match the id type", indices->esz);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n == 0 || k == 0) {
+    if (nnz != nullptr) {
+      zero_total_kernel<<<1, 1, 0, s>>>(nnz);
+      DGS_LAUNCH_CHECK();
+    }
+    return DGS_OK;
+  }
+  DGS_REQUIRE(out_capacity == 0 || (coo_row != nullptr && coo_col != nullptr), DGS_ERR_INVALID,
+              "dgs_sample_uniform: null output");
+  const PlanView pv = plan_view(const_cast<void*>(plan), n);
+  const uint64_t key = mix64(rng_seed) ^ mix64(rng_offset ^ 0xA5A5A5A55A5A5A5Aull);
+  rc = ids64 ? launch_uniform<int64_t>(*indices, seeds, n, k, replace != 0, pv, key, coo_row, coo_col,
+                                       out_capacity, picked_pos, status, s)
+             : launch_uniform<int32_t>(*indices, seeds, n, k, replace != 0, pv, key, coo_row, coo_col,
+                                       out_capacity, picked_pos, status, s);
+  if (rc != DGS_OK) return rc;
+  if (nnz != nullptr) {
+    copy_total_kernel<<<1, 1, 0, s>>>(pv.total, nnz);
+    DGS_LAUNCH_CHECK();
+  }
+  return DGS_OK;
+}
+
+extern "C" int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chunk_desc* probs,
+                                   const void* seeds, int32_t ids64, int64_t n, int64_t k,
+                                   int32_t replace, const void* plan, uint64_t rng_seed,
+                                   uint64_t rng_offset, void* coo_row, void* coo_col,
+                                   int64_t out_capacity, int64_t* nnz, int64_t* picked_pos,
+                                   int32_t* status, dgs_stream_t stream) {
+  using namespace dgs;
+  int rc = validate_desc(indices, "dgs_sample_weighted");
+  if (rc != DGS_OK) return rc;
+  rc = validate_desc(probs, "dgs_sample_weighted(probs)");
+  if (rc != DGS_OK) return rc;
+  rc = check_sample_args("dgs_sample_weighted", seeds, n, k, plan);
+  if (rc != DGS_OK) return rc;
+  DGS_REQUIRE(indices->esz == (ids64 ? 8 : 4), DGS_ERR_INVALID,
+              "dgs_sample_weighted: indices element size %d does not match the id type", indices->esz);
+  DGS_REQUIRE(probs->esz == 4, DGS_ERR_UNSUPPORTED, "dgs_sample_weighted: weights must be fp32");
+  // the reference asserts the same bound on the device (rowwise_sampling_probs.cu:65)
+  DGS_REQUIRE(replace || k <= 32, DGS_ERR_UNSUPPORTED,
+              "dgs_sample_weighted: k=%lld > 32 without replacement is not supported", (long long)k);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n == 0 || k == 0) {
+    if (nnz != nullptr) {
+      zero_total_kernel<<<1, 1, 0, s>>>(nnz);
+      DGS_LAUNCH_CHECK();
+    }
+    return DGS_OK;
+  }
+  DGS_REQUIRE(out_capacity == 0 || (coo_row != nullptr && coo_col != nullptr), DGS_ERR_INVALID,
+              "dgs_sample_weighted: null output");
+  const PlanView pv = plan_view(const_cast<void*>(plan), n);
+  const uint64_t key = mix64(rng_seed) ^ mix64(rng_offset ^ 0xA5A5A5A55A5A5A5Aull);
+  const unsigned grid = static_cast<unsigned>(pv.ntiles);
+  if (ids64)
+    sample_weighted_kernel<int64_t><<<grid, SAMPLE_BLOCK, 0, s>>>(
+        *indices, *probs, static_cast<const int64_t*>(seeds), n, k, replace != 0, pv.row_begin, pv.deg,
+        pv.tile_off, key, static_cast<int64_t*>(coo_row), static_cast<int64_t*>(coo_col), out_capacity,
+        picked_pos, status);
+  else
+    sample_weighted_kernel<int32_t><<<grid, SAMPLE_BLOCK, 0, s>>>(
+        *indices, *probs, static_cast<const int32_t*>(seeds), n, k, replace != 0, pv.row_begin, pv.deg,
+        pv.tile_off, key, static_cast<int32_t*>(coo_row), static_cast<int32_t*>(coo_col), out_capacity,
+        picked_pos, status);
+  DGS_LAUNCH_CHECK();
+  if (nnz != nullptr) {
+    copy_total_kernel<<<1, 1, 0, s>>>(pv.total, nnz);
+    DGS_LAUNCH_CHECK();
+  }
+  return DGS_OK;
+}

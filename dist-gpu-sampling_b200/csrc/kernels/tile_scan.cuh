@@ -1,0 +1,47 @@
+// Exclusive scan of per-tile sums: the middle step of every "count per tile ->
+// scan tile sums -> write with known offsets" sequence in this library (sample
+// offsets, first-occurrence numbering, split-index classes).  Replaces the
+// reference's cub::DeviceScan wrapper (src/cuda/cub_function.h:10-22) plus its
+// blocking read-back of the last element (src/cuda/rowwise_sampling.cu:147,
+// src/cuda/tensor_reindex.cu:129): the totals go straight to a caller-supplied
+// (normally pinned) location, so the host reads them whenever it next
+// synchronises instead of stalling mid-sequence.
+#pragma once
+#include "common.cuh"
+
+namespace dgs {
+
+constexpr int TILE_SCAN_BLOCK = 1024;
+
+// sums: [ntiles][C] tile-major.  In place: sums[t][c] becomes the exclusive
+// prefix over tiles; totals_dev[c] (device scratch, optional) and
+// totals_out[c] (optional) receive the grand totals.  One CTA.
+template <int C>
+__global__ void __launch_bounds__(TILE_SCAN_BLOCK)
+tile_scan_kernel(int64_t* __restrict__ sums, const int64_t ntiles, int64_t* __restrict__ totals_dev,
+                 int64_t* __restrict__ totals_out) {
+  __shared__ int64_t smem[TILE_SCAN_BLOCK / 32 + 1];
+  int64_t carry[C];
+#pragma unroll
+  for (int c = 0; c < C; ++c) carry[c] = 0;
+  for (int64_t t0 = 0; t0 < ntiles; t0 += TILE_SCAN_BLOCK) {
+    const int64_t t = t0 + threadIdx.x;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const int64_t v = (t < ntiles) ? sums[t * C + c] : 0;
+      int64_t total;
+      const int64_t ex = block_exclusive_scan<int64_t, TILE_SCAN_BLOCK>(v, smem, &total);
+      if (t < ntiles) sums[t * C + c] = carry[c] + ex;
+      carry[c] += total;
+    }
+  }
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      if (totals_dev != nullptr) totals_dev[c] = carry[c];
+      if (totals_out != nullptr) totals_out[c] = carry[c];
+    }
+  }
+}
+
+}  // namespace dgs
