@@ -1,0 +1,371 @@
+"""Benchmark of the hot path: 3-hop neighbour sampling + relabel + feature gather.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                  [--workload products|small] [--batch 1024]
+
+One step = one mini-batch per rank through the reference-facing operators:
+  for fan_out in reversed([15, 10, 5]):  sample_neighbors_with_chunk_tensor -> tensor_relabel
+  x = features._CAPI_index(input_nodes)
+on a Products-shaped synthetic graph (2,449,029 nodes, ~123.7 M edges, Chung-Lu
+power law, 100 fp32 features per node) whose indptr / indices / features live in
+ChunkTensors split evenly over the N GPUs of the node (weak scaling: every rank
+samples its own 1,024-seed batches).
+
+Printed JSON (rank 0, one line):
+  value      sampled edges/s of the whole job, device-timed, seeds resident in HBM;
+             the timed step is sample + relabel + gather
+  e2e        same metric with the seeds coming from pinned host memory and a
+             device->host read of the result inside the timed region
+  roofline   the gather kernel: algorithmic bytes / CUDA-event time vs measured HBM peak
+  cpu_baseline  the CPU oracle (port of the reference algorithm) on a bounded sample
+
+`--impl reference` times that CPU port alone on all host threads (the reference
+project has no CPU implementation of its own and its DGL baseline is not
+installable here).
+"""
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FANOUTS = [15, 10, 5]
+WORKLOADS = {
+    # name: (nodes, mean degree, gamma, feature dim, train set size)
+    "products": (2_449_029, 50.5, 2.1, 100, 196_615),
+    "small": (100_000, 20.0, 2.1, 64, 20_000),
+}
+# kernels of this library launched per operator call (memsets are not kernels)
+LAUNCHES_SAMPLE = 4   # plan, tile scan, sample, total copy
+LAUNCHES_RELABEL = 5  # insert, count, tile scan, number, lookup
+LAUNCHES_GATHER = 1
+# DRAM bytes per gathered row (read + write) from the ncu capture summarised in
+# profiles/; None until a capture exists for the benchmarked row width
+NCU_TRAFFIC_BYTES_PER_ROW = {100: None}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="products", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=1024)
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self, lo=0, hi=None):
+        """Summary of the samples [lo, hi) taken while the timed region ran
+        (all samples if that window is empty because the region was too short)."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        window = self.rows[lo:hi] if hi is not None and hi > lo else self.rows
+        all_rows, self.rows = self.rows, window
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i] == "Active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm), "samples_total": len(all_rows)}
+
+
+def build_graph(workload, device):
+    """Same seeded graph on every rank (generated on `device`)."""
+    synth = importlib.import_module("dist-gpu-sampling_b200.synth")
+    nodes, mean_deg, gamma, dim, train = WORKLOADS[workload]
+    indptr, indices = synth.chung_lu_csc(nodes, mean_deg, gamma, seed=11, device=device)
+    return indptr, indices, nodes, dim, train
+
+
+def make_features(nodes, dim, device):
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(3)
+    return torch.randn(nodes, dim, generator=g, device=device, dtype=torch.float32)
+
+
+def config_dict(args, n_edges_graph, world):
+    nodes, mean_deg, gamma, dim, train = WORKLOADS[args.workload]
+    return {"workload": "%s-shaped synthetic: %d nodes, %d edges (Chung-Lu gamma=%.1f), CSC int64, "
+                        "features [%d,%d] fp32" % (args.workload, nodes, n_edges_graph, gamma, nodes, dim),
+            "fanouts": FANOUTS, "batch_per_rank": args.batch, "global_batch": args.batch * world,
+            "train_set": train, "replace": False,
+            "step": "3 x (sample_neighbors_with_chunk_tensor + tensor_relabel) + features._CAPI_index(input_nodes)",
+            "storage": "indptr/indices/features in ChunkTensors split evenly over %d GPU(s), no host tail" % world,
+            "l2": "inputs larger than L2 (indices %.2f GB, features %.2f GB); a new seed batch every step"
+                  % (n_edges_graph * 8 / 1e9, nodes * dim * 4 / 1e9)}
+
+
+# ---------------------------------------------------------------------------
+# CPU arm (oracle port): used by --impl reference and by the cpu_baseline leg
+# ---------------------------------------------------------------------------
+def cpu_step(o, indptr, indices, feats, seeds):
+    frontier, blocks, edges = o.sample_blocks(indptr, indices, seeds, FANOUTS)
+    x = o.index_flat(feats, frontier)
+    return edges, frontier.size, x
+
+
+def run_cpu(args, indptr, indices, feats, batches, steps, warmup, budget_s=None):
+    from oracle import oracle as o
+    o.build()
+    for b in range(warmup):
+        cpu_step(o, indptr, indices, feats, batches[b % len(batches)])
+    edges, t0, done = 0, time.perf_counter(), 0
+    for b in range(steps):
+        e, _, _ = cpu_step(o, indptr, indices, feats, batches[(warmup + b) % len(batches)])
+        edges += e
+        done += 1
+        if budget_s is not None and time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return edges / dt, dt / done * 1e3, done, o.num_threads()
+
+
+def main_reference(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    synth = importlib.import_module("dist-gpu-sampling_b200.synth")
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    indptr, indices, nodes, dim, train = build_graph(args.workload, dev)
+    n_edges_graph = int(indices.numel())
+    feats = make_features(nodes, dim, dev).cpu().numpy()
+    indptr, indices = indptr.cpu().numpy(), indices.cpu().numpy()
+    batches = synth.train_batches(nodes, train, args.batch)
+    value, ms, done, threads = run_cpu(args, indptr, indices, feats, batches, args.steps, args.warmup)
+    line = {"impl": "reference", "metric": "sampled_edges_per_s", "value": value, "unit": "edges/s",
+            "n_gpus": args.gpus, "steps": done, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
+            "data": "synthetic", "config": config_dict(args, n_edges_graph, args.gpus),
+            "cpu_baseline": {"value": value, "unit": "edges/s", "cores": threads, "kind": "port",
+                             "sample": "%d batches of %d seeds (one per step), CPU restatement of the reference's "
+                                       "sample->relabel loop + index_select, OpenMP over seeds" % (done, args.batch)},
+            "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def main_ours(args):
+    import torch
+    import torch.distributed as dist
+    pkg = importlib.import_module("dist-gpu-sampling_b200")
+    synth = importlib.import_module("dist-gpu-sampling_b200.synth")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    pkg.load_ops()
+    if world > 1:
+        pkg.create_dgs_communicator(world)
+    ops = torch.ops.dgs_ops
+
+    # ---- data: same graph on every rank, each rank keeps its own chunk ----
+    indptr, indices, nodes, dim, train = build_graph(args.workload, dev)
+    n_edges_graph = int(indices.numel())
+    feats = make_features(nodes, dim, dev)
+
+    def to_chunk(t):
+        nbytes = t.numel() * t.element_size()
+        cap = -(-nbytes // world)
+        cap = -(-cap // 16) * 16
+        ct = torch.classes.dgs_classes.ChunkTensor(list(t.shape), t.dtype, cap)
+        sub = ct._CAPI_get_sub_device_tensor()
+        flat = t.reshape(-1)
+        lo = rank * sub.numel()
+        n = max(0, min(sub.numel(), flat.numel() - lo))
+        if n > 0:
+            sub[:n].copy_(flat[lo:lo + n])
+        return ct
+
+    c_indptr, c_indices, c_feats = to_chunk(indptr), to_chunk(indices), to_chunk(feats)
+    host_graph = None
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        host_graph = (indptr.cpu().numpy(), indices.cpu().numpy(), feats.cpu().numpy())
+    del indptr, indices, feats
+    torch.cuda.empty_cache()
+    if world > 1:
+        dist.barrier()
+
+    batches_np = synth.train_batches(nodes, train, args.batch)
+    nb = batches_np.shape[0]
+    my = [b for b in range(nb) if b % world == rank]           # disjoint batches per rank
+    host_batches = torch.from_numpy(batches_np).pin_memory()
+    dev_batches = host_batches.to(dev)
+    torch.manual_seed(1234 + rank)
+
+    def step(seeds):
+        frontier, blocks, n_edges = pkg.sample_blocks(seeds, FANOUTS, c_indptr, c_indices)
+        return frontier, n_edges
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    clocks = ClockSampler(local_rank)
+    if rank == 0:
+        clocks.start()
+    # ---- warm-up ----
+    for s in range(args.warmup):
+        fr, _ = step(dev_batches[my[s % len(my)]])
+        c_feats._CAPI_index(fr)
+
+    # ---- timed: K steps, seeds resident on the device ----
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    n_before = len(clocks.rows)
+    t_begin = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    edges = rows = 0
+    t_begin.record()
+    for s in range(args.steps):
+        seeds = dev_batches[my[(args.warmup + s) % len(my)]]
+        ev[s][0].record()
+        fr, e = step(seeds)
+        ev[s][1].record()
+        x = c_feats._CAPI_index(fr)
+        ev[s][2].record()
+        edges += e
+        rows += fr.numel()
+    t_end.record()
+    barrier()
+    n_after = len(clocks.rows)
+    total_ms = t_begin.elapsed_time(t_end)
+    sample_ms = sum(a.elapsed_time(b) for a, b, _ in ev)
+    gather_ms = sum(b.elapsed_time(c) for _, b, c in ev)
+
+    # ---- end to end: seeds from pinned host memory, result read back ----
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e2e_edges, d2h = 0, 0
+    e0.record()
+    for s in range(args.steps):
+        seeds = host_batches[my[(args.warmup + s) % len(my)]].to(dev, non_blocking=True)
+        fr, e = step(seeds)
+        x = c_feats._CAPI_index(fr)
+        chk = torch.stack([x.sum(), fr.sum().to(torch.float32)]).cpu()   # the step's result leaves the device
+        e2e_edges += e
+        d2h = chk.numel() * 4 + 8 * (2 * len(FANOUTS))                    # + the sizes every operator reads back
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    clock_info = clocks.stop(n_before, n_after) if rank == 0 else None
+
+    # ---- reduce over ranks: max time, summed work ----
+    stats = torch.tensor([total_ms, sample_ms, gather_ms, e2e_ms], dtype=torch.float64, device=dev)
+    work = torch.tensor([edges, rows, e2e_edges], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    total_ms, sample_ms, gather_ms, e2e_ms = stats.tolist()
+    edges_all, rows_all, e2e_edges_all = work.tolist()
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        row_alg_bytes = 8 + 2 * dim * 4
+        rows_per_launch = rows / args.steps
+        gather_ms_launch = gather_ms / args.steps
+        achieved = rows_per_launch * row_alg_bytes / (gather_ms_launch * 1e-3) / 1e9
+        per_row = NCU_TRAFFIC_BYTES_PER_ROW.get(dim)
+        line = {
+            "metric": "sampled_edges_per_s", "value": edges_all / (total_ms * 1e-3), "unit": "edges/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
+            "data": "synthetic", "config": config_dict(args, n_edges_graph, world),
+            "breakdown": {"sample_relabel_ms_per_step": sample_ms / args.steps,
+                          "gather_ms_per_step": gather_ms / args.steps,
+                          "sampling_only_edges_per_s": edges_all / (sample_ms * 1e-3),
+                          "edges_per_step_per_rank": edges / args.steps,
+                          "input_nodes_per_step_per_rank": rows_per_launch,
+                          "gather_payload_gbs_all_ranks": rows_all * dim * 4 / (gather_ms * 1e-3) / 1e9},
+            "e2e": {"value": e2e_edges_all / (e2e_ms * 1e-3), "unit": "edges/s",
+                    "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * (len(FANOUTS) * (LAUNCHES_SAMPLE + LAUNCHES_RELABEL) + LAUNCHES_GATHER),
+            "roofline": {"kernel": "gather_rows_kernel (features._CAPI_index)", "bound": "hbm",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_row": row_alg_bytes,
+                         "rows_per_launch": rows_per_launch, "ms_per_launch": gather_ms_launch,
+                         "traffic": per_row * rows_per_launch if per_row else None},
+            "clocks": clock_info,
+        }
+        if host_graph is not None:
+            v, ms, done, threads = run_cpu(args, host_graph[0], host_graph[1], host_graph[2], batches_np,
+                                           steps=10 ** 6, warmup=1, budget_s=args.cpu_seconds)
+            line["cpu_baseline"] = {"value": v, "unit": "edges/s", "cores": threads, "kind": "port",
+                                    "sample": "%d batches of %d seeds in %.1f s (same graph and step)"
+                                              % (done, args.batch, done * ms / 1e3)}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line), flush=True)
+    del c_indptr, c_indices, c_feats     # collective teardown, same order on every rank
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        main_reference(a)
+    else:
+        main_ours(a)

@@ -96,7 +96,7 @@ def build_abi(force=False, verbose=False, ptxas_info=False):
         objs.append(obj)
     if relink:
         cmd = [_nvcc(), "-shared", "-cudart", "shared", "-o", abi_path()] + objs + [
-            "-lnccl", "-Xlinker", "-rpath", "-Xlinker", "/usr/local/cuda/lib64"]
+            "-ldl", "-Xlinker", "-rpath", "-Xlinker", "/usr/local/cuda/lib64"]
         log += _run(cmd, verbose)
     return log
 

@@ -360,9 +360,9 @@ dgs_segments make_segments(const std::vector<torch::Tensor>& ts, std::vector<tor
 std::tuple<torch::Tensor, std::vector<torch::Tensor>> TensorRelabelCUDA(
     std::vector<torch::Tensor> mapping_tensors, std::vector<torch::Tensor> requiring_relabel_tensors) {
   TORCH_CHECK(!mapping_tensors.empty(), "_CAPI_tensor_relabel: no mapping tensors");
-  check_status("_CAPI_tensor_relabel");
   const torch::Tensor& first = mapping_tensors[0];
   CHECK_CUDA(first);
+  check_status("_CAPI_tensor_relabel");
   const bool ids64 = is_id64(first, "mapping tensors");
   for (const auto& t : mapping_tensors)
     TORCH_CHECK(t.device() == first.device() && t.scalar_type() == first.scalar_type(),

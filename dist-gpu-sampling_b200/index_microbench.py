@@ -1,0 +1,158 @@
+"""ChunkTensor index micro-benchmark: GB/s per location class.
+
+The tool the reference ships as python/compute_loading_factor.py (written
+against a constructor that no longer exists there), rebuilt on the real
+operator API: one [rows, dim] fp32 table split over the GPUs of the node plus
+an optional pinned host tail; random row ids are split with _CAPI_split_index
+and each class is gathered with _CAPI_local_index / _CAPI_remote_index /
+_CAPI_host_index, plus the mixed _CAPI_index.  Instead of the reference's
+assumed bandwidths (1300 / 260 / 31 GB/s, :110-122) every class is compared
+with a bandwidth measured on the machine it runs on.
+
+  python dist-gpu-sampling_b200/index_microbench.py --rows 4000000 --dim 128 --n 1000000
+  python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
+      dist-gpu-sampling_b200/index_microbench.py --rows 8000000 --host-frac 0.2
+
+The table is filled in place, chunk by chunk, with a hash of the flat element
+index, so every gathered row can be verified without a second copy.
+Prints one JSON object per measured case (rank 0).
+"""
+import argparse
+import importlib
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=4_000_000)
+    ap.add_argument("--dim", type=int, default=128)
+    ap.add_argument("--n", type=int, default=1_000_000, help="row ids per query")
+    ap.add_argument("--host-frac", type=float, default=0.0, help="fraction of rows kept in the host tail")
+    ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"])
+    ap.add_argument("--misalign", type=int, default=0, help="extra bytes of capacity: rows straddle chunks")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--hbm-peak", type=float, default=0.0, help="GB/s; 0 = measure a device copy here")
+    args = ap.parse_args()
+
+    import torch
+    import torch.distributed as dist
+    pkg = importlib.import_module("dist-gpu-sampling_b200")
+    synth = importlib.import_module("dist-gpu-sampling_b200.synth")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg.load_ops()
+    if world > 1:
+        pkg.create_dgs_communicator(world)
+
+    D, rows = args.dim, args.rows
+    gpu_rows = int(rows * (1.0 - args.host_frac))
+    cap = -(-gpu_rows // world) * D * 4 + args.misalign
+    table = torch.classes.dgs_classes.ChunkTensor([rows, D], torch.float32, cap)
+    sub = table._CAPI_get_sub_device_tensor()
+    each = sub.numel()
+    step = 1 << 26
+    for lo in range(0, each, step):
+        n = min(step, each - lo)
+        sub[lo:lo + n] = synth.hashed_values(rank * each + lo, n, device=dev)
+    host = table._CAPI_get_host_tensor()
+    if rank == 0 and host.numel():
+        thr = rows * D - host.numel()
+        for lo in range(0, host.numel(), step):
+            n = min(step, host.numel() - lo)
+            host[lo:lo + n] = synth.hashed_values(thr + lo, n, device=dev).cpu()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(100 + rank)
+    if args.dist == "uniform":
+        ids = torch.randint(0, rows, (args.n,), device=dev, generator=g)
+    else:  # Zipf(1.1) ranks by inverse CDF, rank -> row through a fixed permutation
+        u = torch.rand(args.n, device=dev, generator=g, dtype=torch.float64)
+        a = 1.1
+        r = ((1.0 - u * (1.0 - float(rows) ** (1.0 - a))) ** (1.0 / (1.0 - a))).floor().clamp_(1, rows).long() - 1
+        gp = torch.Generator(device=dev)
+        gp.manual_seed(7)
+        ids = torch.randperm(rows, device=dev, generator=gp)[r]
+
+    def timed(fn, idx):
+        for _ in range(args.warmup):
+            out = fn(idx)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(args.iters + 1)]
+        e[0].record()
+        for i in range(args.iters):
+            out = fn(idx)
+            e[i + 1].record()
+        torch.cuda.synchronize()
+        ms = sorted(e[i].elapsed_time(e[i + 1]) for i in range(args.iters))
+        return out, ms[len(ms) // 2]
+
+    # measured denominators
+    hbm = args.hbm_peak
+    if hbm <= 0:
+        a_ = torch.empty(1 << 28, dtype=torch.float32, device=dev)
+        b_ = torch.empty_like(a_)
+        _, ms = timed(lambda _: b_.copy_(a_), None)
+        hbm = 2 * a_.numel() * 4 / ms / 1e6
+        del a_, b_
+    host_link = None
+    if host.numel():
+        src = torch.empty(1 << 26, dtype=torch.float32).pin_memory()
+        dst = torch.empty(1 << 26, dtype=torch.float32, device=dev)
+        _, ms = timed(lambda _: dst.copy_(src, non_blocking=True), None)
+        host_link = src.numel() * 4 / ms / 1e6
+
+    lo_ids, re_ids, ho_ids = table._CAPI_split_index(ids)
+    _, split_ms = timed(table._CAPI_split_index, ids)
+
+    def verify(out, idx):
+        k = min(2048, idx.numel())
+        if k == 0:
+            return True
+        sel = idx[:k]
+        flat = (sel[:, None] * D + torch.arange(D, device=dev)[None, :]).reshape(-1)
+        exp = synth.hash_of_index(flat).reshape(k, D)
+        return bool(torch.equal(out[:k], exp))
+
+    cases = [("index (mixed)", table._CAPI_index, ids, None),
+             ("local_index", table._CAPI_local_index, lo_ids, hbm),
+             ("remote_index", table._CAPI_remote_index, re_ids, 770.0),
+             ("host_index", table._CAPI_host_index, ho_ids, host_link)]
+    for name, fn, idx, peak in cases:
+        if idx.numel() == 0:
+            continue
+        out, ms = timed(fn, idx)
+        payload = idx.numel() * D * 4
+        line = {"case": name, "rank": rank, "world": world, "rows": idx.numel(), "dim": D, "dist": args.dist,
+                "ms": ms, "payload_gbs": payload / ms / 1e6,
+                "algorithmic_gbs": idx.numel() * (8 + 2 * D * 4) / ms / 1e6, "verified": verify(out, idx)}
+        if name == "local_index":
+            line.update(bound="hbm", peak_gbs=hbm, frac=line["algorithmic_gbs"] / hbm)
+        elif peak:
+            line.update(bound="nvlink" if name == "remote_index" else "host link", peak_gbs=peak,
+                        frac=line["payload_gbs"] / peak)
+        else:
+            line.update(class_sizes={"local": lo_ids.numel(), "remote": re_ids.numel(), "host": ho_ids.numel()},
+                        split_index_ms=split_ms)
+        if rank == 0 or name != "index (mixed)":
+            print(json.dumps(line), flush=True)
+    del table, sub, host
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

