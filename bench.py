@@ -43,12 +43,12 @@ WORKLOADS = {
     "small": (100_000, 20.0, 2.1, 64, 20_000),
 }
 # kernels of this library launched per operator call (memsets are not kernels)
-LAUNCHES_SAMPLE = 4   # plan, tile scan, sample, total copy
-LAUNCHES_RELABEL = 5  # insert, count, tile scan, number, lookup
+LAUNCHES_SAMPLE = 2   # plan (+ tile scan in its last CTA), sample
+LAUNCHES_RELABEL = 4  # insert, count (+ tile scan in its last CTA), number, lookup
 LAUNCHES_GATHER = 1
 # DRAM bytes per gathered row (read + write) from the ncu capture summarised in
 # profiles/; None until a capture exists for the benchmarked row width
-NCU_TRAFFIC_BYTES_PER_ROW = {100: None}
+NCU_TRAFFIC_BYTES_PER_ROW = {100: 860.7}
 
 
 def parse_args():

@@ -72,6 +72,34 @@ void check_status(const char* where) {
 
 cudaStream_t current_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
 
+// Data-dependent sizes: the host marks a pinned word as pending, a kernel early
+// in the operator's sequence overwrites it, and the host picks the value up as
+// soon as it lands -- the kernels enqueued behind that one keep running while
+// the operator returns (the reference stalls on a blocking device read in the
+// middle of its sequence instead: src/cuda/rowwise_sampling.cu:147,
+// src/cuda/tensor_reindex.cu:129).
+constexpr int64_t kPending = INT64_MIN;
+
+int64_t wait_size(volatile int64_t* word, cudaStream_t stream, const char* where) {
+  for (uint64_t spins = 1;; ++spins) {
+    int64_t v = *word;
+    if (v != kPending) return v;
+    if ((spins & 0x3FF) == 0) {
+      // also the way out if the stream died: never spin on a value that cannot arrive
+      const cudaError_t q = cudaStreamQuery(stream);
+      if (q == cudaSuccess) {
+        v = *word;
+        TORCH_CHECK(v != kPending, "dgs: ", where, ": the stream finished without reporting a size");
+        return v;
+      }
+      TORCH_CHECK(q == cudaErrorNotReady, "dgs: ", where, ": CUDA error while waiting: ", cudaGetErrorString(q));
+    }
+#if defined(__x86_64__)
+    __builtin_ia32_pause();
+#endif
+  }
+}
+
 void sync_stream() {
   TORCH_CHECK(cudaStreamSynchronize(current_stream()) == cudaSuccess, "dgs: stream synchronisation failed: ",
               cudaGetErrorString(cudaGetLastError()));
@@ -187,7 +215,7 @@ class ChunkTensor : public torch::CustomClassHolder {
     torch::Tensor out = torch::empty_like(index);
     const size_t sb = dgs_split_index_scratch_bytes(n);
     torch::Tensor scratch = byte_scratch(sb, index.device());
-    int64_t* counts = host_words().sizes;
+    int64_t* counts = host_words().sizes + 4;
     DGS_CHECK_RC(dgs_split_index(&desc_, index.data_ptr(), ids64, n, elem_stride_, out.data_ptr(), counts,
                                  scratch.data_ptr(), sb, current_stream()));
     sync_stream();
@@ -264,15 +292,16 @@ std::tuple<torch::Tensor, torch::Tensor> sample_impl(torch::Tensor seeds, const 
   torch::Tensor row, col;
   int64_t nnz = 0;
   if (one_shot) {
-    // everything is enqueued before the host waits once for the size
+    // everything is enqueued first; the host then only waits for the plan
+    // kernel's total, not for the sampling kernel behind it
     const int64_t cap = n * k;
     row = torch::empty({cap}, opt);
     col = torch::empty({cap}, opt);
-    DGS_CHECK_RC(dgs_sample_plan(&indptr, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), nullptr,
+    w.sizes[0] = kPending;
+    DGS_CHECK_RC(dgs_sample_plan(&indptr, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), w.sizes,
                                  w.status, stream));
-    run(row, col, cap, w.sizes);
-    sync_stream();
-    nnz = w.sizes[0];
+    run(row, col, cap, nullptr);
+    nnz = wait_size(w.sizes, stream, "sample_neighbors");
     check_status("sample_neighbors");
     TORCH_CHECK(nnz >= 0 && nnz <= cap, "dgs: sampler returned an impossible size");
     return std::make_tuple(row.narrow(0, 0, nnz), col.narrow(0, 0, nnz));
@@ -390,11 +419,13 @@ std::tuple<torch::Tensor, std::vector<torch::Tensor>> TensorRelabelCUDA(
   torch::Tensor table = byte_scratch(tb, first.device());
   torch::Tensor uniq = torch::empty({n_keys}, first.options());
   torch::Tensor out = torch::empty({n_req}, first.options());
-  DGS_CHECK_RC(dgs_unique_first_occurrence(&keys, ids64, table.data_ptr(), tb, uniq.data_ptr(), w.sizes,
+  // the count kernel reports the number of distinct keys; the numbering and
+  // lookup kernels behind it are still in flight when this returns
+  w.sizes[1] = kPending;
+  DGS_CHECK_RC(dgs_unique_first_occurrence(&keys, ids64, table.data_ptr(), tb, uniq.data_ptr(), w.sizes + 1,
                                            w.status, stream));
   DGS_CHECK_RC(dgs_relabel_lookup(table.data_ptr(), tb, n_keys, &req, ids64, out.data_ptr(), stream));
-  sync_stream();
-  const int64_t nu = w.sizes[0];
+  const int64_t nu = wait_size(w.sizes + 1, stream, "_CAPI_tensor_relabel");
   check_status("_CAPI_tensor_relabel");
   TORCH_CHECK(nu >= 0 && nu <= n_keys, "dgs: relabel returned an impossible size");
   return std::make_tuple(uniq.narrow(0, 0, nu), out.split_with_sizes(split_sizes, 0));

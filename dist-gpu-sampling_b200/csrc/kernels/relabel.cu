@@ -17,7 +17,8 @@
 //   * inputs are read through a segment list instead of being concatenated.
 //   * the insert pass remembers each input's slot, so later passes index the
 //     table directly instead of probing again.
-//   * numbering is count-per-tile -> scan of tile sums -> write; the label is
+//   * numbering is count-per-tile (the last CTA to finish scans the tile sums,
+//     no extra launch) -> write; the label is
 //     stored into the slot's value with the top bit set, which can never be
 //     mistaken for an input index by a concurrent reader, so no third table.
 //   * the number of distinct keys goes to a caller-supplied (pinned) word.
@@ -45,6 +46,7 @@ struct TableView {
   uint32_t* slot_of;   // [n]  slot of every input
   int64_t* tile_off;   // [ntiles]
   int64_t* total;      // [1]
+  unsigned int* ticket;  // [1]
   uint64_t cap;
   int64_t ntiles;
 };
@@ -68,6 +70,7 @@ inline TableView table_view(void* mem, int64_t n) {
   p += align_up(static_cast<size_t>(n) * sizeof(uint32_t), 16);
   t.tile_off = reinterpret_cast<int64_t*>(p);
   t.total = t.tile_off + t.ntiles;
+  t.ticket = reinterpret_cast<unsigned int*>(t.total + 1);
   return t;
 }
 
@@ -116,11 +119,15 @@ relabel_insert_kernel(const __grid_constant__ dgs_segments keys, const int64_t n
     atomicMin(&slots[found].val, static_cast<unsigned long long>(i));
 }
 
-// pass 2: input i is a first occurrence iff the stored minimum equals i
+// pass 2: input i is a first occurrence iff the stored minimum equals i;
+// the last CTA to finish turns the per-tile counts into offsets and publishes
+// the number of distinct keys
 __global__ void __launch_bounds__(RL_BLOCK)
 relabel_count_kernel(const int64_t n, const Slot* __restrict__ slots,
-                     const uint32_t* __restrict__ slot_of, int64_t* __restrict__ tile_sums) {
+                     const uint32_t* __restrict__ slot_of, int64_t* tile_sums, unsigned int* ticket,
+                     int64_t* total_dev, int64_t* n_unique_out) {
   __shared__ int s_cnt;
+  __shared__ int64_t s_scan[RL_BLOCK / 32 + 1];
   if (threadIdx.x == 0) s_cnt = 0;
   __syncthreads();
   const int64_t base = static_cast<int64_t>(blockIdx.x) * RL_TILE + threadIdx.x * RL_ITEMS;
@@ -137,7 +144,8 @@ relabel_count_kernel(const int64_t n, const Slot* __restrict__ slots,
   for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(FULL_MASK, c, o);
   if ((threadIdx.x & 31) == 0 && c) atomicAdd(&s_cnt, c);
   __syncthreads();
-  if (threadIdx.x == 0) tile_sums[blockIdx.x] = s_cnt;
+  publish_and_scan_tiles<RL_BLOCK>(static_cast<int64_t>(s_cnt), tile_sums, ticket, total_dev, n_unique_out,
+                                   s_scan);
 }
 
 // pass 3: number the first occurrences, emit them, store the label in the slot
@@ -223,12 +231,12 @@ template <typename IdT>
 int run_unique(const dgs_segments& keys, int64_t n, const TableView& t, void* unique_out,
                int64_t* n_unique, int32_t* status, cudaStream_t s) {
   DGS_CUDA_TRY(cudaMemsetAsync(t.slots, 0xFF, t.cap * sizeof(Slot), s));
+  DGS_CUDA_TRY(cudaMemsetAsync(t.ticket, 0, sizeof(unsigned int), s));
   const unsigned per_key_grid = static_cast<unsigned>((n + RL_BLOCK - 1) / RL_BLOCK);
   relabel_insert_kernel<IdT><<<per_key_grid, RL_BLOCK, 0, s>>>(keys, n, t.slots, t.cap - 1, t.slot_of, status);
   DGS_LAUNCH_CHECK();
-  relabel_count_kernel<<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(n, t.slots, t.slot_of, t.tile_off);
-  DGS_LAUNCH_CHECK();
-  tile_scan_kernel<1><<<1, TILE_SCAN_BLOCK, 0, s>>>(t.tile_off, t.ntiles, t.total, n_unique);
+  relabel_count_kernel<<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(n, t.slots, t.slot_of, t.tile_off,
+                                                                            t.ticket, t.total, n_unique);
   DGS_LAUNCH_CHECK();
   relabel_number_kernel<IdT><<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(
       keys, n, t.slots, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out));
@@ -244,7 +252,7 @@ extern "C" size_t dgs_relabel_table_bytes(int64_t n) {
   if (n < 0) n = 0;
   const int64_t ntiles = (n + RL_TILE - 1) / RL_TILE;
   return table_capacity(n) * sizeof(Slot) + align_up(static_cast<size_t>(n) * sizeof(uint32_t), 16) +
-         static_cast<size_t>(ntiles + 1) * sizeof(int64_t);
+         static_cast<size_t>(ntiles + 2) * sizeof(int64_t);
 }
 
 extern "C" int dgs_unique_first_occurrence(const dgs_segments* keys, int32_t ids64, void* table,

@@ -33,8 +33,14 @@
 //   * weighted sampling with replacement builds no cumulative array in global
 //     memory: the row is streamed twice through a warp scan and each draw is
 //     resolved by a ballot in the 32-edge window it falls into.
-//   * counts, offsets and the total are produced on the device; the total goes
-//     to a caller-supplied (pinned) word, so there is no mid-sequence stall.
+//   * counts, offsets and the total come from ONE plan kernel: every CTA scans
+//     its 256 seeds and the CTA that finishes last (an atomic ticket, nobody
+//     waits) scans the per-tile sums; the total goes to a caller-supplied
+//     (pinned) word, so the host learns the output size while the sampling
+//     kernel is still running.
+//   * the sampling kernels give every seed its own group / warp and never loop
+//     over seeds, so even a 1 024-seed hop fills the machine with independent
+//     short chains instead of a few long ones.
 #include "common.cuh"
 #include "philox.cuh"
 #include "tile_scan.cuh"
@@ -54,8 +60,10 @@ constexpr uint32_t TAG_WREPL = 0x57524550u;
 struct PlanView {
   int64_t* row_begin;  // [n]
   int64_t* deg;        // [n]
-  int64_t* tile_off;   // [ntiles]  per-tile sums, scanned in place
+  int64_t* local_off;  // [n]       exclusive prefix of the counts inside the seed's 256-tile
+  int64_t* tile_off;   // [ntiles]  per-tile sums, scanned in place by the last CTA
   int64_t* total;      // [1]
+  unsigned int* ticket;  // [1]     CTAs that have published their tile sum
   int64_t ntiles;
 };
 
@@ -64,8 +72,10 @@ inline PlanView plan_view(void* plan, int64_t n) {
   v.ntiles = (n + SAMPLE_TILE - 1) / SAMPLE_TILE;
   v.row_begin = static_cast<int64_t*>(plan);
   v.deg = v.row_begin + n;
-  v.tile_off = v.deg + n;
+  v.local_off = v.deg + n;
+  v.tile_off = v.local_off + n;
   v.total = v.tile_off + v.ntiles;
+  v.ticket = reinterpret_cast<unsigned int*>(v.total + 1);
   return v;
 }
 
@@ -81,7 +91,8 @@ __global__ void __launch_bounds__(SAMPLE_BLOCK)
 sample_plan_kernel(const __grid_constant__ dgs_chunk_desc indptr, const IdT* __restrict__ seeds,
                    const int64_t n, const int64_t k, const bool replace,
                    int64_t* __restrict__ row_begin, int64_t* __restrict__ deg_out,
-                   int64_t* __restrict__ tile_sums, int32_t* __restrict__ status) {
+                   int64_t* __restrict__ local_off, int64_t* tile_sums, int64_t* total_out,
+                   unsigned int* ticket, int64_t* nnz_out, int32_t* __restrict__ status) {
   __shared__ int64_t smem[SAMPLE_BLOCK / 32 + 1];
   constexpr int sh = sizeof(IdT) == 8 ? 3 : 2;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + threadIdx.x;
@@ -108,8 +119,11 @@ sample_plan_kernel(const __grid_constant__ dgs_chunk_desc indptr, const IdT* __r
     cnt = pick_count(deg, k, replace);
   }
   int64_t total;
-  block_exclusive_scan<int64_t, SAMPLE_BLOCK>(cnt, smem, &total);
-  if (threadIdx.x == 0) tile_sums[blockIdx.x] = total;
+  const int64_t ex = block_exclusive_scan<int64_t, SAMPLE_BLOCK>(cnt, smem, &total);
+  if (i < n) local_off[i] = ex;
+
+  // publish the tile sum; the CTA that draws the last ticket scans all of them
+  publish_and_scan_tiles<SAMPLE_BLOCK>(total, tile_sums, ticket, total_out, nnz_out, smem);
 }
 
 // ---------------------------------------------------------------------------
@@ -143,25 +157,21 @@ struct Emit {
   }
 };
 
-// Phase A of both sampling kernels: per-seed output offsets of this tile.
-__device__ __forceinline__ void tile_offsets(const int64_t* __restrict__ plan_rb,
-                                             const int64_t* __restrict__ plan_deg,
-                                             const int64_t* __restrict__ tile_off, int64_t n,
-                                             int64_t k, bool replace, int64_t* s_off, int64_t* s_rb,
-                                             int64_t* s_deg, int64_t* s_scan) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + threadIdx.x;
-  int64_t deg = 0, rb = 0;
-  if (i < n) {
-    deg = plan_deg[i];
-    rb = plan_rb[i];
+// What a group / warp needs to know about its seed.
+struct SeedPlan {
+  int64_t rb, deg, o;
+};
+__device__ __forceinline__ SeedPlan seed_plan(const int64_t* __restrict__ plan_rb,
+                                              const int64_t* __restrict__ plan_deg,
+                                              const int64_t* __restrict__ local_off,
+                                              const int64_t* __restrict__ tile_off, int64_t i, bool valid) {
+  SeedPlan p{0, 0, 0};
+  if (valid) {
+    p.rb = plan_rb[i];
+    p.deg = plan_deg[i];
+    p.o = tile_off[i / SAMPLE_TILE] + local_off[i];
   }
-  int64_t total;
-  const int64_t ex =
-      block_exclusive_scan<int64_t, SAMPLE_BLOCK>(pick_count(deg, k, replace), s_scan, &total);
-  s_off[threadIdx.x] = tile_off[blockIdx.x] + ex;
-  s_rb[threadIdx.x] = rb;
-  s_deg[threadIdx.x] = deg;
-  __syncthreads();
+  return p;
 }
 
 // ---------------------------------------------------------------------------
@@ -172,15 +182,11 @@ __global__ void __launch_bounds__(SAMPLE_BLOCK)
 sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT* __restrict__ seeds,
                       const int64_t n, const int64_t k, const bool replace,
                       const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
-                      const int64_t* __restrict__ tile_off, const uint64_t key,
-                      IdT* coo_row, IdT* coo_col, const int64_t out_capacity,
+                      const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
+                      const uint64_t key, IdT* coo_row, IdT* coo_col, const int64_t out_capacity,
                       int64_t* __restrict__ picked_pos, int32_t* __restrict__ status) {
-  __shared__ int64_t s_off[SAMPLE_TILE], s_rb[SAMPLE_TILE], s_deg[SAMPLE_TILE];
-  __shared__ int64_t s_scan[SAMPLE_BLOCK / 32 + 1];
-  tile_offsets(plan_rb, plan_deg, tile_off, n, k, replace, s_off, s_rb, s_deg, s_scan);
-
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
-  constexpr int GROUPS = SAMPLE_BLOCK / G;
+  constexpr int GROUPS = SAMPLE_BLOCK / G;  // seeds per CTA
   const int lane = threadIdx.x & 31;
   const int l = threadIdx.x % G;        // lane inside the group
   const int group = threadIdx.x / G;    // group inside the CTA
@@ -188,10 +194,11 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
   const unsigned gmask = (G == 32) ? FULL_MASK : (((1u << G) - 1u) << (gw * G));
   const bool fast = !replace && k <= G;  // uniform over the grid
 
-  for (int sl = group; sl < SAMPLE_TILE; sl += GROUPS) {  // same trip count for every group
-    const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + sl;
+  {  // one seed per group; all 32 lanes of a warp walk through the same code
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * GROUPS + group;
     const bool valid = i < n;
-    const int64_t deg = s_deg[sl], rb = s_rb[sl], o = s_off[sl];
+    const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, valid);
+    const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
     const int64_t seed = valid ? static_cast<int64_t>(seeds[i]) : 0;
     const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
 
@@ -201,7 +208,7 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
           const Philox4 r = philox4x32_10(key, i_lo, i_hi, static_cast<uint32_t>(t), TAG_REPLACE);
           emit(o, t, seed, rb, static_cast<int64_t>(bounded(r, static_cast<uint64_t>(deg))));
         }
-      continue;
+      return;
     }
 
     if (fast) {
@@ -257,11 +264,11 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
       } else if (valid && !sampled) {
         if (l < deg) emit(o, l, seed, rb, l);  // whole row, CSC order (deg <= k <= G)
       }
-      continue;
+      return;
     }
 
     // -- general k (> G is only possible with G == 32: the group is the warp) --
-    if (!valid) continue;
+    if (!valid) return;
     if (deg <= k) {
       for (int64_t t = l; t < deg; t += G) emit(o, t, seed, rb, t);
     } else if (o + k > out_capacity) {
@@ -302,13 +309,9 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
                        const __grid_constant__ dgs_chunk_desc probs, const IdT* __restrict__ seeds,
                        const int64_t n, const int64_t k, const bool replace,
                        const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
-                       const int64_t* __restrict__ tile_off, const uint64_t key, IdT* coo_row,
-                       IdT* coo_col, const int64_t out_capacity, int64_t* __restrict__ picked_pos,
-                       int32_t* __restrict__ status) {
-  __shared__ int64_t s_off[SAMPLE_TILE], s_rb[SAMPLE_TILE], s_deg[SAMPLE_TILE];
-  __shared__ int64_t s_scan[SAMPLE_BLOCK / 32 + 1];
-  tile_offsets(plan_rb, plan_deg, tile_off, n, k, replace, s_off, s_rb, s_deg, s_scan);
-
+                       const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
+                       const uint64_t key, IdT* coo_row, IdT* coo_col, const int64_t out_capacity,
+                       int64_t* __restrict__ picked_pos, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
   const int l = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -317,21 +320,22 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
   const float FLOOR_ZERO_W = -3.402823466e+38f;  // weight <= 0: behind every positive weight
   const float FLOOR_POS_W = -3.0e+38f;           // clamp for positive weights
 
-  for (int sl = warp; sl < SAMPLE_TILE; sl += WARPS) {
-    const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + sl;
-    if (i >= n) break;  // warp-uniform
-    const int64_t deg = s_deg[sl], rb = s_rb[sl], o = s_off[sl];
+  {  // one seed per warp
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * WARPS + warp;
+    if (i >= n) return;  // warp-uniform
+    const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, true);
+    const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
     const int64_t seed = static_cast<int64_t>(seeds[i]);
     const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
-    if (deg <= 0) continue;
+    if (deg <= 0) return;
 
     if (!replace && deg <= k) {
       for (int64_t t = l; t < deg; t += 32) emit(o, t, seed, rb, t);
-      continue;
+      return;
     }
     if (rb + deg > probs.total) {
       if (l == 0) raise_status(status, DGS_ERR_RANGE);
-      continue;
+      return;
     }
     int64_t run;
     const char* wp = resolve(probs, 2, rb, &run);
@@ -438,10 +442,10 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
 template <typename IdT>
 int launch_plan(const dgs_chunk_desc& indptr, const void* seeds, int64_t n, int64_t k, bool replace,
                 const PlanView& pv, int64_t* nnz, int32_t* status, cudaStream_t s) {
+  DGS_CUDA_TRY(cudaMemsetAsync(pv.ticket, 0, sizeof(unsigned int), s));
   sample_plan_kernel<IdT><<<static_cast<unsigned>(pv.ntiles), SAMPLE_BLOCK, 0, s>>>(
-      indptr, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.tile_off, status);
-  DGS_LAUNCH_CHECK();
-  tile_scan_kernel<1><<<1, TILE_SCAN_BLOCK, 0, s>>>(pv.tile_off, pv.ntiles, pv.total, nnz);
+      indptr, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
+      pv.tile_off, pv.total, pv.ticket, nnz, status);
   DGS_LAUNCH_CHECK();
   return DGS_OK;
 }
@@ -453,11 +457,11 @@ template <typename IdT>
 int launch_uniform(const dgs_chunk_desc& indices, const void* seeds, int64_t n, int64_t k,
                    bool replace, const PlanView& pv, uint64_t key, void* coo_row, void* coo_col,
                    int64_t cap, int64_t* pos, int32_t* status, cudaStream_t s) {
-  const unsigned grid = static_cast<unsigned>(pv.ntiles);
-#define DGS_LAUNCH_U(G)                                                                          \
-  sample_uniform_kernel<IdT, G><<<grid, SAMPLE_BLOCK, 0, s>>>(                                   \
-      indices, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.tile_off, \
-      key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, status)
+#define DGS_LAUNCH_U(G)                                                                            \
+  sample_uniform_kernel<IdT, G>                                                                    \
+      <<<static_cast<unsigned>((n + SAMPLE_BLOCK / G - 1) / (SAMPLE_BLOCK / G)), SAMPLE_BLOCK, 0, s>>>( \
+          indices, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off, \
+          pv.tile_off, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, status)
   if (k <= 4) DGS_LAUNCH_U(4);
   else if (k <= 8) DGS_LAUNCH_U(8);
   else if (k <= 16) DGS_LAUNCH_U(16);
@@ -470,8 +474,7 @@ int launch_uniform(const dgs_chunk_desc& indices, const void* seeds, int64_t n, 
 int check_sample_args(const char* who, const void* seeds, int64_t n, int64_t k, const void* plan) {
   DGS_REQUIRE(n >= 0 && k >= 0, DGS_ERR_INVALID, "%s: n=%lld k=%lld", who, (long long)n, (long long)k);
   DGS_REQUIRE(n == 0 || (seeds != nullptr && plan != nullptr), DGS_ERR_INVALID, "%s: null buffer", who);
-  DGS_REQUIRE((n + SAMPLE_TILE - 1) / SAMPLE_TILE <= 0x7fffffffLL, DGS_ERR_UNSUPPORTED,
-              "%s: too many seeds", who);
+  DGS_REQUIRE(n / (SAMPLE_BLOCK / 32) < 0x7fffffffLL, DGS_ERR_UNSUPPORTED, "%s: too many seeds", who);
   return DGS_OK;
 }
 
@@ -481,7 +484,7 @@ int check_sample_args(const char* who, const void* seeds, int64_t n, int64_t k, 
 extern "C" size_t dgs_sample_plan_bytes(int64_t n) {
   if (n < 0) n = 0;
   const int64_t ntiles = (n + dgs::SAMPLE_TILE - 1) / dgs::SAMPLE_TILE;
-  return static_cast<size_t>(2 * n + ntiles + 1) * sizeof(int64_t);
+  return static_cast<size_t>(3 * n + ntiles + 2) * sizeof(int64_t);
 }
 
 extern "C" int dgs_sample_plan(const dgs_chunk_desc* indptr, const void* seeds, int32_t ids64,
@@ -574,16 +577,16 @@ extern "C" int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chun
               "dgs_sample_weighted: null output");
   const PlanView pv = plan_view(const_cast<void*>(plan), n);
   const uint64_t key = mix64(rng_seed) ^ mix64(rng_offset ^ 0xA5A5A5A55A5A5A5Aull);
-  const unsigned grid = static_cast<unsigned>(pv.ntiles);
+  const unsigned grid = static_cast<unsigned>((n + SAMPLE_BLOCK / 32 - 1) / (SAMPLE_BLOCK / 32));
   if (ids64)
     sample_weighted_kernel<int64_t><<<grid, SAMPLE_BLOCK, 0, s>>>(
         *indices, *probs, static_cast<const int64_t*>(seeds), n, k, replace != 0, pv.row_begin, pv.deg,
-        pv.tile_off, key, static_cast<int64_t*>(coo_row), static_cast<int64_t*>(coo_col), out_capacity,
+        pv.local_off, pv.tile_off, key, static_cast<int64_t*>(coo_row), static_cast<int64_t*>(coo_col), out_capacity,
         picked_pos, status);
   else
     sample_weighted_kernel<int32_t><<<grid, SAMPLE_BLOCK, 0, s>>>(
         *indices, *probs, static_cast<const int32_t*>(seeds), n, k, replace != 0, pv.row_begin, pv.deg,
-        pv.tile_off, key, static_cast<int32_t*>(coo_row), static_cast<int32_t*>(coo_col), out_capacity,
+        pv.local_off, pv.tile_off, key, static_cast<int32_t*>(coo_row), static_cast<int32_t*>(coo_col), out_capacity,
         picked_pos, status);
   DGS_LAUNCH_CHECK();
   if (nnz != nullptr) {

@@ -44,4 +44,43 @@ tile_scan_kernel(int64_t* __restrict__ sums, const int64_t ntiles, int64_t* __re
   }
 }
 
+
+// The same scan without a second launch: every CTA of a counting kernel calls
+// this after computing its tile sum.  The CTA that draws the last ticket (an
+// atomic counter that must be zero at launch; nobody waits on anybody) scans
+// all tile sums in place and publishes the total.  `smem` needs BLOCK/32 + 1
+// entries; must be called by all threads of the CTA.
+template <int BLOCK>
+__device__ __forceinline__ void publish_and_scan_tiles(int64_t my_tile_sum, int64_t* tile_sums,
+                                                       unsigned int* ticket, int64_t* total_dev,
+                                                       int64_t* total_out, int64_t* smem) {
+  __shared__ bool s_last;
+  if (threadIdx.x == 0) {
+    tile_sums[blockIdx.x] = my_tile_sum;
+    __threadfence();
+    s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int64_t ntiles = gridDim.x;
+  int64_t carry = 0;
+  for (int64_t t0 = 0; t0 < ntiles; t0 += BLOCK) {
+    const int64_t t = t0 + threadIdx.x;
+    const int64_t v = t < ntiles ? __ldcg(tile_sums + t) : 0;
+    int64_t sum;
+    const int64_t e = block_exclusive_scan<int64_t, BLOCK>(v, smem, &sum);
+    if (t < ntiles) tile_sums[t] = carry + e;
+    carry += sum;
+  }
+  if (threadIdx.x == 0) {
+    if (total_dev != nullptr) *total_dev = carry;
+    *ticket = 0;
+    if (total_out != nullptr) {
+      *total_out = carry;
+      __threadfence_system();
+    }
+  }
+}
+
 }  // namespace dgs

@@ -9,7 +9,7 @@ _CAPI_host_index, plus the mixed _CAPI_index.  Instead of the reference's
 assumed bandwidths (1300 / 260 / 31 GB/s, :110-122) every class is compared
 with a bandwidth measured on the machine it runs on.
 
-  python dist-gpu-sampling_b200/index_microbench.py --rows 4000000 --dim 128 --n 1000000
+  python dist-gpu-sampling_b200/index_microbench.py --rows 4000000 --dim 128 --ids 1000000
   python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
       dist-gpu-sampling_b200/index_microbench.py --rows 8000000 --host-frac 0.2
 
@@ -31,7 +31,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, default=4_000_000)
     ap.add_argument("--dim", type=int, default=128)
-    ap.add_argument("--n", type=int, default=1_000_000, help="row ids per query")
+    ap.add_argument("--ids", type=int, default=1_000_000, help="row ids per query")
     ap.add_argument("--host-frac", type=float, default=0.0, help="fraction of rows kept in the host tail")
     ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"])
     ap.add_argument("--misalign", type=int, default=0, help="extra bytes of capacity: rows straddle chunks")
@@ -78,9 +78,9 @@ def main():
     g = torch.Generator(device=dev)
     g.manual_seed(100 + rank)
     if args.dist == "uniform":
-        ids = torch.randint(0, rows, (args.n,), device=dev, generator=g)
+        ids = torch.randint(0, rows, (args.ids,), device=dev, generator=g)
     else:  # Zipf(1.1) ranks by inverse CDF, rank -> row through a fixed permutation
-        u = torch.rand(args.n, device=dev, generator=g, dtype=torch.float64)
+        u = torch.rand(args.ids, device=dev, generator=g, dtype=torch.float64)
         a = 1.1
         r = ((1.0 - u * (1.0 - float(rows) ** (1.0 - a))) ** (1.0 / (1.0 - a))).floor().clamp_(1, rows).long() - 1
         gp = torch.Generator(device=dev)

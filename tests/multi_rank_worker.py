@@ -1,0 +1,99 @@
+"""Worker run under torchrun by test_gpu_multi.py: one process per GPU.
+
+Every rank builds the same seeded data, so each can check what it reads from
+its own chunk, from peer chunks (cudaIpc mappings over NVLink) and from the
+shared host tail against the CPU oracle.  Prints "RANK r OK" on success.
+"""
+import importlib
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from oracle import oracle as o  # noqa: E402
+
+
+def main():
+    pkg = importlib.import_module("dist-gpu-sampling_b200")
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    pkg.load_ops()
+    pkg.create_dgs_communicator(world)
+    ops = torch.ops.dgs_ops
+    rng = np.random.default_rng(5)          # same stream on every rank
+
+    # ---- a mismatching constructor call fails on every rank, nobody hangs ----
+    try:
+        torch.classes.dgs_classes.ChunkTensor([100, 4], torch.float32, 160 + 16 * rank)
+        raise SystemExit("rank %d: mismatching metadata was accepted" % rank)
+    except RuntimeError as e:
+        assert "differs" in str(e) or "rejected" in str(e), str(e)
+
+    # ---- feature table: chunks on every GPU + host tail, rows straddle boundaries ----
+    rows, D = 6000, 100
+    table = rng.standard_normal((rows, D)).astype(np.float32)
+    cap = 4 * (D * (rows // (world + 1)) + 36)            # not row aligned; ~1/(world+1) of the rows on the host
+    ct = pkg.create_chunktensor(torch.from_numpy(table), world, cap, cache_rate=1.0)
+    cm = o.ChunkModel([rows, D], np.float32, min(cap, table.nbytes // world), world=world)
+    cm.load(table)
+    assert cm.host_n > 0
+    sub = ct._CAPI_get_sub_device_tensor().cpu().numpy()
+    assert sub.tobytes() == cm.sub_device_tensor(rank).tobytes(), "local chunk differs"
+    assert ct._CAPI_get_host_tensor().numpy().tobytes() == cm.host_tensor().tobytes(), "host tail differs"
+    idx = np.concatenate([rng.integers(0, rows, size=20000), np.arange(rows)])
+    idx_t = torch.from_numpy(idx).to(dev)
+    out = ct._CAPI_index(idx_t)
+    assert out.cpu().numpy().tobytes() == table[idx].tobytes(), "index differs from index_select"
+    lo, re, ho = ct._CAPI_split_index(idx_t)
+    elo, ere, eho = cm.split_index(idx, rank)
+    assert lo.tolist() == elo.tolist() and re.tolist() == ere.tolist() and ho.tolist() == eho.tolist()
+    assert re.numel() > 0
+    for part, fn in ((lo, ct._CAPI_local_index), (re, ct._CAPI_remote_index), (ho, ct._CAPI_host_index)):
+        assert fn(part).cpu().numpy().tobytes() == table[part.cpu().numpy()].tobytes()
+    del fn, part                                   # bound methods keep the ChunkTensor alive
+
+    # ---- graph in ChunkTensors over all ranks: sample + relabel per rank ----
+    synth = importlib.import_module("dist-gpu-sampling_b200.synth")
+    indptr, indices = synth.uniform_graph_csc(20000, 300000, seed=1)
+    probs = np.random.default_rng(6).random(indices.size).astype(np.float32) + 0.01
+    big = 1 << 40
+    c_ip = pkg.create_chunktensor(torch.from_numpy(indptr), world, big)
+    c_ix = pkg.create_chunktensor(torch.from_numpy(indices), world, big, cache_rate=0.8)
+    c_pr = pkg.create_chunktensor(torch.from_numpy(probs), world, big, cache_rate=0.8)
+    seeds = np.random.default_rng(100 + rank).permutation(20000)[:2048]      # each rank its own batch
+    sd = torch.from_numpy(seeds).to(dev)
+    edge_keys = np.repeat(np.arange(20000), np.diff(indptr)) * 20000 + indices
+    torch.manual_seed(rank)
+    for weighted in (False, True):
+        cur, cur_np = sd, seeds
+        for k in (10, 5):
+            if weighted:
+                row, col = ops._CAPI_sample_neighbors_with_probs_with_chunk_tensor(cur, c_ip, c_ix, c_pr, k, False)
+            else:
+                row, col = ops._CAPI_sample_neighbors_with_chunk_tensor(cur, c_ip, c_ix, k, False)
+            r_np, c_np = row.cpu().numpy(), col.cpu().numpy()
+            out_ptr, nnz = o.sample_counts(indptr, cur_np, k, False)
+            assert r_np.size == nnz and np.array_equal(r_np, np.repeat(cur_np, np.diff(out_ptr)))
+            assert np.isin(r_np * 20000 + c_np, edge_keys).all(), "sampled a non-edge"
+            frontier, (rr, cc) = ops._CAPI_tensor_relabel([cur, col], [row, col])
+            eu, (er, ec) = o.tensor_relabel([cur_np, c_np], [r_np, c_np])
+            assert frontier.tolist() == eu.tolist() and rr.tolist() == er.tolist() and cc.tolist() == ec.tolist()
+            cur, cur_np = frontier, eu
+    assert torch.ops.dgs_ops._CAPI_get_current_allocated() > 0
+    torch.cuda.synchronize()
+    dist.barrier()
+    del ct, c_ip, c_ix, c_pr, sub          # collective teardown, same order everywhere
+    assert torch.ops.dgs_ops._CAPI_get_current_allocated() == 0
+    dist.barrier()
+    print("RANK %d OK" % rank, flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
