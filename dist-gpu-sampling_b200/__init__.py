@@ -96,6 +96,7 @@ ABI_SIGNATURES = {
     "dgs_gather_rows": (ctypes.c_int, [_DP, _I32, _VP, _I32, _I64, _I64, _VP, _VP, _VP]),
     "dgs_split_index_scratch_bytes": (_SZ, [_I64]),
     "dgs_split_index": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _VP, _VP, _VP, _SZ, _VP]),
+    "dgs_split_index_static": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _VP, _VP, _VP]),
     "dgs_sample_plan_bytes": (_SZ, [_I64]),
     "dgs_sample_plan": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _I32, _VP, _VP, _VP, _VP]),
     "dgs_sample_uniform": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _I32, _VP, _U64, _U64, _VP, _VP,

@@ -14,6 +14,8 @@
 //   remote : everything else
 // Output is one array [local ids | remote ids | host ids], each class in input
 // order, and the three class sizes.
+#include <mutex>
+
 #include "common.cuh"
 #include "tile_scan.cuh"
 
@@ -116,6 +118,34 @@ __global__ void zero_counts_kernel(int64_t* counts) {
   if (threadIdx.x < 3) counts[threadIdx.x] = 0;
 }
 
+// ---- scratch for dgs_split_index_static ---------------------------------------
+// Lives in the library image: every GPU that loads the library holds these
+// 192 KB until the process exits.  Layout as in run_split: [tiles][3] counts,
+// then 3 totals.
+constexpr int64_t SPLIT_STATIC_WORDS = (DGS_SPLIT_STATIC_MAX_IDS / SPLIT_TILE) * 3 + 3;
+static __device__ __align__(256) int64_t g_split_static[SPLIT_STATIC_WORDS];
+
+// In host code `g_split_static` is only a handle for the runtime, not an
+// address a kernel may use; the device address is looked up once per device,
+// with that device current.
+int split_static_scratch(int64_t** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int64_t* addr[kMaxDevices] = {};
+  int dev = -1;
+  DGS_CUDA_TRY(cudaGetDevice(&dev));
+  DGS_REQUIRE(dev >= 0 && dev < kMaxDevices, DGS_ERR_UNSUPPORTED, "device index %d is not supported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    DGS_CUDA_TRY(cudaGetSymbolAddress(&p, g_split_static));
+    DGS_REQUIRE(p != nullptr, DGS_ERR_CUDA, "no device address for the static split scratch");
+    addr[dev] = static_cast<int64_t*>(p);
+  }
+  *out = addr[dev];
+  return DGS_OK;
+}
+
 }  // namespace
 }  // namespace dgs
 
@@ -150,4 +180,34 @@ extern "C" int dgs_split_index(const dgs_chunk_desc* t, const void* idx, int32_t
   b.loc_hi = static_cast<int64_t>(t->local_rank + 1) * t->each / D;
   return ids64 ? run_split<int64_t>(idx, n, b, out, counts, static_cast<int64_t*>(scratch), s)
                : run_split<int32_t>(idx, n, b, out, counts, static_cast<int64_t*>(scratch), s);
+}
+
+extern "C" int dgs_split_index_static(const dgs_chunk_desc* t, const void* idx, int32_t ids64, int64_t n,
+                                      int64_t D, void* out, int64_t* counts, dgs_stream_t stream) {
+  using namespace dgs;
+  int rc = validate_desc(t, "dgs_split_index_static");
+  if (rc != DGS_OK) return rc;
+  DGS_REQUIRE(n >= 0 && D >= 1 && counts != nullptr, DGS_ERR_INVALID, "dgs_split_index_static: bad arguments");
+  DGS_REQUIRE(n <= DGS_SPLIT_STATIC_MAX_IDS, DGS_ERR_UNSUPPORTED,
+              "dgs_split_index_static: %lld ids exceed the built-in scratch (at most %lld per call); "
+              "use dgs_split_index with caller-provided scratch",
+              (long long)n, (long long)DGS_SPLIT_STATIC_MAX_IDS);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n == 0) {
+    zero_counts_kernel<<<1, 32, 0, s>>>(counts);
+    DGS_LAUNCH_CHECK();
+    return DGS_OK;
+  }
+  DGS_REQUIRE(idx != nullptr && out != nullptr, DGS_ERR_INVALID, "dgs_split_index_static: null buffer");
+  int64_t* scratch = nullptr;
+  rc = split_static_scratch(&scratch);  // first call on a device: looks the address up
+  if (rc != DGS_OK) return rc;
+  SplitBounds b;
+  b.host_lo = t->threshold / D;
+  b.loc_lo = static_cast<int64_t>(t->local_rank) * t->each / D;
+  b.loc_hi = static_cast<int64_t>(t->local_rank + 1) * t->each / D;
+  // every scratch word a call reads (tile counts, totals) is written earlier in
+  // the same call, so nothing left over from the previous call needs clearing
+  return ids64 ? run_split<int64_t>(idx, n, b, out, counts, scratch, s)
+               : run_split<int32_t>(idx, n, b, out, counts, scratch, s);
 }

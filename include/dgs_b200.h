@@ -148,6 +148,31 @@ DGS_API int dgs_split_index(const dgs_chunk_desc* t, const void* idx, int32_t id
                     int64_t n, int64_t D, void* out, int64_t* counts,
                     void* scratch, size_t scratch_bytes, dgs_stream_t stream);
 
+/* Same result as dgs_split_index, for hosts that must not allocate: the three
+ * kernels keep their tile counters in a 192 KB array that is part of the
+ * library image instead of caller scratch, and the call itself performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.  It is meant
+ * for callers that receive all their buffers up front and then run with the
+ * allocator off limits -- a plug-in inside a serving process with a fixed
+ * memory budget, or a latency-critical loop that cannot afford the
+ * device-wide synchronisation cudaMalloc and cudaFree may cause.  `out` and
+ * `counts` are still supplied by the caller.
+ * Limits and rules:
+ *   - at most DGS_SPLIT_STATIC_MAX_IDS ids per call; larger n is rejected with
+ *     DGS_ERR_UNSUPPORTED before anything is launched;
+ *   - the first call on each device looks up the array's device address (with
+ *     that device current); make that first call before any stream capture;
+ *   - all calls on one device share the one array, which keeps whatever the
+ *     previous call left in it: calls whose kernels can overlap on the GPU
+ *     (different streams without ordering between them) race and must be
+ *     serialised by the caller.  Nothing has to be cleared between calls:
+ *     every word a call reads it has written itself.
+ * This entry point has no counterpart in the reference. */
+#define DGS_SPLIT_STATIC_MAX_IDS (1 << 24)
+DGS_API int dgs_split_index_static(const dgs_chunk_desc* t, const void* idx, int32_t ids64,
+                                   int64_t n, int64_t D, void* out, int64_t* counts,
+                                   dgs_stream_t stream);
+
 /* ---- row-wise neighbour sampling --------------------------------------- */
 /* Plan = per-seed row range and output offsets.
  * _GetSubIndptr + cub_exclusiveSum, src/cuda/rowwise_sampling.cu:13-40 and the
