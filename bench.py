@@ -1,7 +1,7 @@
 """Benchmark of the hot path: 3-hop neighbour sampling + relabel + feature gather.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload products|small] [--batch 1024]
+                  [--workload products|papers100m|small] [--batch 1024]
 
 One step = one mini-batch per rank through the reference-facing operators:
   for fan_out in reversed([15, 10, 5]):  sample_neighbors_with_chunk_tensor -> tensor_relabel
@@ -9,7 +9,9 @@ One step = one mini-batch per rank through the reference-facing operators:
 on a Products-shaped synthetic graph (2,449,029 nodes, ~123.7 M edges, Chung-Lu
 power law, 100 fp32 features per node) whose indptr / indices / features live in
 ChunkTensors split evenly over the N GPUs of the node (weak scaling: every rank
-samples its own 1,024-seed batches).
+samples its own 1,024-seed batches).  `--workload papers100m` is the
+Papers100M-shaped configuration (111 M nodes, ~1.6 B edges, 128 features: 70 GB,
+which fits one B200 or is split over N).
 
 Printed JSON (rank 0, one line):
   value      sampled edges/s of the whole job, device-timed, seeds resident in HBM;
@@ -40,6 +42,7 @@ FANOUTS = [15, 10, 5]
 WORKLOADS = {
     # name: (nodes, mean degree, gamma, feature dim, train set size)
     "products": (2_449_029, 50.5, 2.1, 100, 196_615),
+    "papers100m": (111_059_956, 14.5, 2.3, 128, 1_207_179),
     "small": (100_000, 20.0, 2.1, 64, 20_000),
 }
 # kernels of this library launched per operator call (memsets are not kernels)
@@ -124,11 +127,21 @@ def build_graph(workload, device):
     return indptr, indices, nodes, dim, train
 
 
+def feature_values(start, count, device):
+    """Feature table element values as a function of the flat element index, so
+    every rank can fill its own chunk in place and nobody holds the table twice."""
+    synth = importlib.import_module("dist-gpu-sampling_b200.synth")
+    return synth.hashed_values(start, count, device=device, salt=3)
+
+
 def make_features(nodes, dim, device):
     import torch
-    g = torch.Generator(device=device)
-    g.manual_seed(3)
-    return torch.randn(nodes, dim, generator=g, device=device, dtype=torch.float32)
+    out = torch.empty(nodes * dim, dtype=torch.float32, device=device)
+    step = 1 << 26
+    for lo in range(0, out.numel(), step):
+        n = min(step, out.numel() - lo)
+        out[lo:lo + n] = feature_values(lo, n, device)
+    return out.view(nodes, dim)
 
 
 def config_dict(args, n_edges_graph, world):
@@ -220,13 +233,14 @@ def main_ours(args):
     # ---- data: same graph on every rank, each rank keeps its own chunk ----
     indptr, indices, nodes, dim, train = build_graph(args.workload, dev)
     n_edges_graph = int(indices.numel())
-    feats = make_features(nodes, dim, dev)
+
+    def chunk_capacity(nbytes):
+        cap = -(-nbytes // world)
+        return -(-cap // 16) * 16
 
     def to_chunk(t):
-        nbytes = t.numel() * t.element_size()
-        cap = -(-nbytes // world)
-        cap = -(-cap // 16) * 16
-        ct = torch.classes.dgs_classes.ChunkTensor(list(t.shape), t.dtype, cap)
+        ct = torch.classes.dgs_classes.ChunkTensor(list(t.shape), t.dtype,
+                                                   chunk_capacity(t.numel() * t.element_size()))
         sub = ct._CAPI_get_sub_device_tensor()
         flat = t.reshape(-1)
         lo = rank * sub.numel()
@@ -235,11 +249,19 @@ def main_ours(args):
             sub[:n].copy_(flat[lo:lo + n])
         return ct
 
-    c_indptr, c_indices, c_feats = to_chunk(indptr), to_chunk(indices), to_chunk(feats)
+    c_indptr, c_indices = to_chunk(indptr), to_chunk(indices)
+    # features: every rank fills its own chunk in place
+    c_feats = torch.classes.dgs_classes.ChunkTensor([nodes, dim], torch.float32, chunk_capacity(nodes * dim * 4))
+    sub = c_feats._CAPI_get_sub_device_tensor()
+    fill = 1 << 26
+    for lo in range(0, min(sub.numel(), max(0, nodes * dim - rank * sub.numel())), fill):
+        n = min(fill, sub.numel() - lo, nodes * dim - rank * sub.numel() - lo)
+        sub[lo:lo + n] = feature_values(rank * sub.numel() + lo, n, dev)
+    del sub
     host_graph = None
-    if rank == 0 and not args.no_cpu_baseline and world == 1:
-        host_graph = (indptr.cpu().numpy(), indices.cpu().numpy(), feats.cpu().numpy())
-    del indptr, indices, feats
+    if rank == 0 and not args.no_cpu_baseline and world == 1 and args.workload != "papers100m":
+        host_graph = (indptr.cpu().numpy(), indices.cpu().numpy(), make_features(nodes, dim, dev).cpu().numpy())
+    del indptr, indices
     torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()

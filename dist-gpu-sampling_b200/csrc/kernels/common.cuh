@@ -70,7 +70,8 @@ __device__ __forceinline__ const char* resolve(const dgs_chunk_desc& d, int sh, 
   int64_t b = d.each;
 #pragma unroll
   for (int q = 1; q < DGS_MAX_PARTS; ++q) {
-    if (q < d.num_parts && e >= b) {
+    if (q >= d.num_parts) break;  // uniform: a plain tensor (one part) skips the chain
+    if (e >= b) {
       p = q;
       base = b;
     }

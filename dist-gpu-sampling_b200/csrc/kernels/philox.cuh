@@ -61,13 +61,14 @@ DGS_HD uint64_t mix64(uint64_t z) {
 DGS_HD uint64_t bounded(const Philox4& r, uint64_t n) {
   if (n <= 0xFFFFFFFFull) {
     const uint32_t n32 = static_cast<uint32_t>(n);
-    const uint32_t thresh = (0u - n32) % n32;  // 2^32 mod n
     uint32_t w[4] = {r.x, r.y, r.z, r.w};
     uint64_t m = 0;
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       m = static_cast<uint64_t>(w[t]) * n32;
-      if (static_cast<uint32_t>(m) >= thresh) break;
+      // the rejection threshold 2^32 mod n costs a division, so it is only
+      // computed in the rare case (probability n / 2^32) where it can matter
+      if (static_cast<uint32_t>(m) >= n32 || static_cast<uint32_t>(m) >= (0u - n32) % n32) break;
     }
     return m >> 32;
   }
@@ -84,6 +85,15 @@ DGS_HD uint64_t bounded(const Philox4& r, uint64_t n) {
   if (static_cast<uint64_t>(p) < thresh) p = static_cast<unsigned __int128>(r1) * n;
   return static_cast<uint64_t>(p >> 64);
 #endif
+}
+
+// One attempt of the same method on a single 32-bit word (n < 2^32): returns
+// false when the word falls into the rejection zone and must be replaced.
+DGS_HD bool bounded_try(uint32_t word, uint32_t n32, uint32_t* out) {
+  const uint64_t m = static_cast<uint64_t>(word) * n32;
+  *out = static_cast<uint32_t>(m >> 32);
+  const uint32_t lo = static_cast<uint32_t>(m);
+  return lo >= n32 || lo >= (0u - n32) % n32;
 }
 
 // uniform float in (0, 1] from 24 random bits (same open/closed ends as

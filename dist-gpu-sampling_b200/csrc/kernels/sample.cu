@@ -219,45 +219,53 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
       const bool active = l < m;
       bool need = active;
       int64_t c = 0;
-      uint32_t round = 0;
-      while (__any_sync(FULL_MASK, need)) {
+      const bool small_row = deg <= 0xFFFFFFFFll;  // every real graph; longer rows take the general path
+      const uint32_t deg32 = static_cast<uint32_t>(deg);
+      Philox4 rnd{0u, 0u, 0u, 0u};
+      for (uint32_t round = 0; __any_sync(FULL_MASK, need); ++round) {
+        // one Philox block per lane feeds four rounds of (re)draws
+        if ((round & 3u) == 0u && active && round < 64)
+          rnd = philox4x32_10(key, i_lo, i_hi, ((round >> 2) << 8) | static_cast<uint32_t>(l), TAG_UNIFORM);
+        bool usable = true;  // false: this attempt hit Lemire's rejection zone, draw again next round
         if (need) {
-          if (round < 64) {
-            const Philox4 r = philox4x32_10(key, i_lo, i_hi, (round << 8) | static_cast<uint32_t>(l), TAG_UNIFORM);
-            c = static_cast<int64_t>(bounded(r, static_cast<uint64_t>(deg)));
-          } else {  // never reached in practice: step to a free neighbour, keeps the loop bounded
+          if (round >= 64) {  // never reached in practice: step to a neighbour, keeps the loop bounded
             c = (c + 1 == deg) ? 0 : c + 1;
+          } else if (small_row) {
+            const uint32_t word = (round & 2u) ? ((round & 1u) ? rnd.w : rnd.z) : ((round & 1u) ? rnd.y : rnd.x);
+            uint32_t pick;
+            usable = bounded_try(word, deg32, &pick);
+            c = pick;
+          } else {
+            const Philox4 r = philox4x32_10(key, i_lo, i_hi, (round << 8) | static_cast<uint32_t>(l), TAG_UNIFORM ^ 1u);
+            c = static_cast<int64_t>(bounded(r, static_cast<uint64_t>(deg)));
           }
         }
+        // lanes holding the same position inside one group see each other; the lowest keeps it
         const unsigned long long tag =
-            active ? (static_cast<unsigned long long>(c) | (static_cast<unsigned long long>(gw) << 58))
-                   : (0x8000000000000000ull | static_cast<unsigned long long>(lane));
+            (active && usable) ? (static_cast<unsigned long long>(c) | (static_cast<unsigned long long>(gw) << 58))
+                               : (0x8000000000000000ull | static_cast<unsigned long long>(lane));
         const unsigned same = __match_any_sync(FULL_MASK, tag);
-        need = active && (__ffs(same) - 1 != lane);
-        if (++round >= 64 + 1024) {
+        need = active && (!usable || (__ffs(same) - 1 != lane));
+        if (round >= 64 + 1024) {
           if (need) raise_status(status, DGS_ERR_TABLE_FULL);
           break;
         }
       }
       if (__any_sync(FULL_MASK, complement)) {
-        // positions a = l and b = l + G cover the row (deg <= 2k <= 2G)
-        const int64_t a = l, b = l + G;
-        bool ex_a = false, ex_b = false;
-#pragma unroll
-        for (int j = 0; j < G; ++j) {
-          const int64_t cj = __shfl_sync(FULL_MASK, c, j, G);
-          if (j < m) {
-            ex_a |= (cj == a);
-            ex_b |= (cj == b);
-          }
+        // the row has at most 2k-1 <= 63 positions: OR the left-out positions of the
+        // group into one 64-bit mask, then every lane ranks its own two positions
+        // (a = l and b = l + G cover the row) among the kept ones -- no shuffles
+        const unsigned long long bit = (complement && active) ? (1ull << c) : 0ull;
+        const unsigned long long out_mask =
+            static_cast<unsigned long long>(__reduce_or_sync(gmask, static_cast<unsigned>(bit))) |
+            (static_cast<unsigned long long>(__reduce_or_sync(gmask, static_cast<unsigned>(bit >> 32))) << 32);
+        if (complement) {
+          const unsigned long long row_mask = (1ull << deg) - 1ull;  // deg <= 63
+          const unsigned long long kept = ~out_mask & row_mask;
+          const int a = l, b = l + G;
+          if ((kept >> a) & 1ull) emit(o, __popcll(kept & ((1ull << a) - 1ull)), seed, rb, a);
+          if (b < 64 && ((kept >> b) & 1ull)) emit(o, __popcll(kept & ((1ull << b) - 1ull)), seed, rb, b);
         }
-        const bool in_a = complement && a < deg && !ex_a;
-        const bool in_b = complement && b < deg && !ex_b;
-        const unsigned ba = __ballot_sync(FULL_MASK, in_a) & gmask;
-        const unsigned bb = __ballot_sync(FULL_MASK, in_b) & gmask;
-        const unsigned lt = (1u << lane) - 1u;
-        if (in_a) emit(o, __popc(ba & lt), seed, rb, a);
-        if (in_b) emit(o, __popc(ba) + __popc(bb & lt), seed, rb, b);
       }
       if (sampled && !complement) {
         if (active) emit(o, l, seed, rb, c);
