@@ -93,15 +93,17 @@ ABI_SIGNATURES = {
     "dgs_store_host_view": (ctypes.c_int, [_VP, ctypes.POINTER(_VP), _I64P]),
     "dgs_store_local_view": (ctypes.c_int, [_VP, ctypes.POINTER(_VP), _I64P]),
     "dgs_alloc_current_bytes": (_I64, []),
-    "dgs_gather_rows": (ctypes.c_int, [_DP, _I32, _VP, _I32, _I64, _I64, _VP, _VP, _VP]),
+    "dgs_locality_order_scratch_bytes": (_SZ, []),
+    "dgs_locality_order": (ctypes.c_int, [_VP, _I32, _I64, _I64, _VP, _VP, _SZ, _VP]),
+    "dgs_gather_rows": (ctypes.c_int, [_DP, _I32, _VP, _I32, _I64, _I64, _VP, _VP, _VP, _VP]),
     "dgs_split_index_scratch_bytes": (_SZ, [_I64]),
     "dgs_split_index": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _VP, _VP, _VP, _SZ, _VP]),
     "dgs_split_index_static": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _VP, _VP, _VP]),
     "dgs_sample_plan_bytes": (_SZ, [_I64]),
     "dgs_sample_plan": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _I32, _VP, _VP, _VP, _VP]),
-    "dgs_sample_uniform": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _I32, _VP, _U64, _U64, _VP, _VP,
+    "dgs_sample_uniform": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _I32, _VP, _VP, _U64, _U64, _VP, _VP,
                                           _I64, _VP, _VP, _VP, _VP]),
-    "dgs_sample_weighted": (ctypes.c_int, [_DP, _DP, _VP, _I32, _I64, _I64, _I32, _VP, _U64, _U64, _VP,
+    "dgs_sample_weighted": (ctypes.c_int, [_DP, _DP, _VP, _I32, _I64, _I64, _I32, _VP, _VP, _U64, _U64, _VP,
                                            _VP, _I64, _VP, _VP, _VP, _VP]),
     "dgs_relabel_table_bytes": (_SZ, [_I64]),
     "dgs_unique_first_occurrence": (ctypes.c_int, [_SP, _I32, _VP, _SZ, _VP, _VP, _VP, _VP]),

@@ -24,6 +24,7 @@ ABI_SOURCES = [
     "kernels/split.cu",
     "kernels/sample.cu",
     "kernels/relabel.cu",
+    "kernels/order.cu",
     "host/error.cc",
     "host/comm.cc",
     "host/store.cc",

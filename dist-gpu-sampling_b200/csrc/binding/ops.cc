@@ -19,6 +19,8 @@
 #include <torch/custom_class.h>
 #include <torch/script.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <tuple>
 #include <vector>
@@ -138,6 +140,29 @@ torch::Tensor byte_scratch(size_t bytes, const torch::Device& dev) {
   return torch::empty({static_cast<int64_t>(bytes)}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
 }
 
+// Visiting a request in address order (dgs_locality_order) is opt-in:
+// DGS_LOCALITY_ORDER=1.  It only pays when address translation limits the
+// request; with chunks allocated in 2 MB units (store.cc) peer reads run at the
+// NVLink rate unordered and the ordering pass would cost a few percent.
+bool wants_locality_order(const dgs_chunk_desc& d, int64_t n) {
+  static const char* env = std::getenv("DGS_LOCALITY_ORDER");
+  (void)d;
+  return env != nullptr && env[0] == '1' && n >= 2 && n <= 0xFFFFFFFFll;
+}
+
+// order tensor (uint32 positions, stored as int32) for `ids`, or an undefined tensor
+torch::Tensor make_locality_order(const dgs_chunk_desc& d, const torch::Tensor& ids, bool ids64, int64_t id_space,
+                                  cudaStream_t stream) {
+  const int64_t n = ids.numel();
+  if (!wants_locality_order(d, n)) return torch::Tensor();
+  torch::Tensor order = torch::empty({n}, torch::TensorOptions().dtype(torch::kInt32).device(ids.device()));
+  const size_t sb = dgs_locality_order_scratch_bytes();
+  torch::Tensor scratch = byte_scratch(sb, ids.device());
+  DGS_CHECK_RC(dgs_locality_order(ids.data_ptr(), ids64, n, std::max<int64_t>(id_space, 1),
+                                  static_cast<uint32_t*>(order.data_ptr()), scratch.data_ptr(), sb, stream));
+  return order;
+}
+
 // (seed, offset) from torch's default CUDA generator, so torch.manual_seed
 // controls sampling; each call consumes one offset step.
 std::pair<uint64_t, uint64_t> next_rng() {
@@ -196,8 +221,11 @@ class ChunkTensor : public torch::CustomClassHolder {
     const int64_t n = index.numel();
     torch::Tensor out =
         torch::empty({n, elem_stride_}, torch::TensorOptions().dtype(dtype_).device(index.device()));
-    DGS_CHECK_RC(dgs_gather_rows(&desc_, location_class, index.data_ptr(), ids64, n, elem_stride_,
-                                 out.data_ptr(), host_words().status, current_stream()));
+    torch::Tensor order =
+        make_locality_order(desc_, index, ids64, desc_.total / std::max<int64_t>(elem_stride_, 1), current_stream());
+    DGS_CHECK_RC(dgs_gather_rows(&desc_, location_class, index.data_ptr(), ids64, n, elem_stride_, out.data_ptr(),
+                                 order.defined() ? static_cast<const uint32_t*>(order.data_ptr()) : nullptr,
+                                 host_words().status, current_stream()));
     return out;
   }
   torch::Tensor Index(torch::Tensor index) { return IndexClass(index, DGS_CLASS_ANY); }
@@ -275,17 +303,20 @@ std::tuple<torch::Tensor, torch::Tensor> sample_impl(torch::Tensor seeds, const 
 
   const size_t pb = dgs_sample_plan_bytes(n);
   torch::Tensor plan = byte_scratch(pb, seeds.device());
+  // CSC rows are stored in node order, so ordering the seeds by id orders the reads of `indices`
+  torch::Tensor order_t = make_locality_order(indices, seeds, ids64, indptr.total - 1, stream);
+  const uint32_t* order = order_t.defined() ? static_cast<const uint32_t*>(order_t.data_ptr()) : nullptr;
   const int64_t esz = ids64 ? 8 : 4;
   const bool one_shot = n * k * 2 * esz <= kOneShotOutputBytes;
 
   auto run = [&](torch::Tensor& row, torch::Tensor& col, int64_t cap, int64_t* nnz) {
     if (probs == nullptr)
-      DGS_CHECK_RC(dgs_sample_uniform(&indices, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(),
+      DGS_CHECK_RC(dgs_sample_uniform(&indices, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), order,
                                       rng.first, rng.second, row.data_ptr(), col.data_ptr(), cap, nnz,
                                       nullptr, w.status, stream));
     else
       DGS_CHECK_RC(dgs_sample_weighted(&indices, probs, seeds.data_ptr(), ids64, n, k, replace,
-                                       plan.data_ptr(), rng.first, rng.second, row.data_ptr(),
+                                       plan.data_ptr(), order, rng.first, rng.second, row.data_ptr(),
                                        col.data_ptr(), cap, nnz, nullptr, w.status, stream));
   };
 

@@ -54,10 +54,18 @@ namespace dgs {
 namespace {
 std::atomic<int64_t> g_allocated{0};
 
+// Chunks are allocated in whole 2 MB units.  A peer that opens the cudaIpc
+// handle of an allocation whose size is not a multiple of 2 MB ends up with a
+// small-page mapping: measured on B200, random 8-byte reads over a 12.8e9-byte
+// peer chunk ran at 75 M/s, over a 13 GiB chunk at 6.4 G/s.  The bookkeeping
+// (dgs_alloc_current_bytes) keeps counting the bytes that were asked for.
+constexpr size_t kChunkGranularity = size_t(2) << 20;
+
 int tracked_malloc(void** p, size_t bytes) {
   *p = nullptr;
   if (bytes == 0) return DGS_OK;
-  DGS_CUDA_TRY(cudaMalloc(p, bytes));
+  const size_t padded = (bytes + kChunkGranularity - 1) / kChunkGranularity * kChunkGranularity;
+  DGS_CUDA_TRY(cudaMalloc(p, padded));
   g_allocated += static_cast<int64_t>(bytes);
   return DGS_OK;
 }

@@ -133,9 +133,11 @@ template <typename Src, int VEC>
 __global__ void __launch_bounds__(GATHER_BLOCK)
 gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int64_t D, const int sh,
                    const uint32_t nvec, const uint32_t rows_per_tile, const uint32_t div_magic,
-                   char* __restrict__ out, int32_t* __restrict__ status) {
+                   char* __restrict__ out, const uint32_t* __restrict__ order,
+                   int32_t* __restrict__ status) {
   using V = typename VecT<VEC>::type;
   __shared__ const char* s_src[GATHER_MAX_ROWS];
+  __shared__ char* s_dst[GATHER_MAX_ROWS];  // only used with a processing order
 
   const int64_t tile_row0 = static_cast<int64_t>(blockIdx.x) * rows_per_tile;
   const uint32_t rows_here =
@@ -144,7 +146,10 @@ gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int6
   // ---- phase 1: one resolution per row -------------------------------------
   bool any_special = false;
   for (uint32_t r = threadIdx.x; r < rows_here; r += GATHER_BLOCK) {
-    const char* src = rows.locate(tile_row0 + r, VEC, status);
+    // with a processing order the r-th row of the tile is request position order[..]
+    const int64_t i = order != nullptr ? static_cast<int64_t>(order[tile_row0 + r]) : tile_row0 + r;
+    const char* src = rows.locate(i, VEC, status);
+    s_dst[r] = out + (i * D << sh);
     any_special |= (reinterpret_cast<uintptr_t>(src) <= 1);
     s_src[r] = src;
   }
@@ -171,10 +176,21 @@ gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int6
         }
       }
     }
+    if (order == nullptr) {
 #pragma unroll
-    for (int u = 0; u < GATHER_UNROLL; ++u) {
-      const uint32_t q = q0 + u * GATHER_BLOCK + threadIdx.x;
-      if (ok[u]) out_tile[q] = v[u];
+      for (int u = 0; u < GATHER_UNROLL; ++u) {
+        const uint32_t q = q0 + u * GATHER_BLOCK + threadIdx.x;
+        if (ok[u]) out_tile[q] = v[u];
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < GATHER_UNROLL; ++u) {
+        const uint32_t q = q0 + u * GATHER_BLOCK + threadIdx.x;
+        if (ok[u]) {
+          const uint32_t r = rows_per_tile == 1 ? 0u : (div_magic ? __umulhi(q, div_magic) : q);
+          reinterpret_cast<V*>(s_dst[r])[q - r * nvec] = v[u];
+        }
+      }
     }
   }
 
@@ -184,12 +200,13 @@ gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int6
     for (uint32_t r = 0; r < rows_here; ++r) {
       const char* src = s_src[r];
       if (reinterpret_cast<uintptr_t>(src) > 1) continue;
-      char* dst = out + ((tile_row0 + r) * D << sh);
+      char* dst = s_dst[r];
+      const int64_t i = (dst - out) / (D << sh);  // request position of this row
       if (src == DGS_ROW_ZERO) {
         for (int64_t b = threadIdx.x; b < (D << sh); b += GATHER_BLOCK) dst[b] = 0;
       } else {
         for (int64_t j = threadIdx.x; j < D; j += GATHER_BLOCK) {
-          const char* p = rows.element(tile_row0 + r, j);
+          const char* p = rows.element(i, j);
           char* q = dst + (j << sh);
           switch (esz) {
             case 8: *reinterpret_cast<uint64_t*>(q) = *reinterpret_cast<const uint64_t*>(p); break;
@@ -204,8 +221,8 @@ gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int6
 }
 
 template <typename Src, int VEC>
-int launch_gather(const Src& rows, int64_t n, int64_t D, int sh, void* out, int32_t* status,
-                  cudaStream_t stream) {
+int launch_gather(const Src& rows, int64_t n, int64_t D, int sh, void* out, const uint32_t* order,
+                  int32_t* status, cudaStream_t stream) {
   const int64_t row_bytes = D << sh;
   const int64_t nvec64 = row_bytes / VEC;
   // the in-tile index q < rows*nvec must keep q*nvec < 2^32 for the magic divide
@@ -221,28 +238,28 @@ int launch_gather(const Src& rows, int64_t n, int64_t D, int sh, void* out, int3
   const int64_t tiles = (n + rows_per_tile - 1) / rows_per_tile;
   DGS_REQUIRE(tiles <= 0x7fffffffLL, DGS_ERR_UNSUPPORTED, "gather: too many rows (%lld)", (long long)n);
   gather_rows_kernel<Src, VEC><<<static_cast<unsigned>(tiles), GATHER_BLOCK, 0, stream>>>(
-      rows, n, D, sh, nvec, rows_per_tile, magic, static_cast<char*>(out), status);
+      rows, n, D, sh, nvec, rows_per_tile, magic, static_cast<char*>(out), order, status);
   DGS_LAUNCH_CHECK();
   return DGS_OK;
 }
 
 template <typename Src>
-int dispatch_vec(int vec, const Src& rows, int64_t n, int64_t D, int sh, void* out, int32_t* status,
-                 cudaStream_t stream) {
+int dispatch_vec(int vec, const Src& rows, int64_t n, int64_t D, int sh, void* out,
+                 const uint32_t* order, int32_t* status, cudaStream_t stream) {
   switch (vec) {
-    case 16: return launch_gather<Src, 16>(rows, n, D, sh, out, status, stream);
-    case 8: return launch_gather<Src, 8>(rows, n, D, sh, out, status, stream);
-    case 4: return launch_gather<Src, 4>(rows, n, D, sh, out, status, stream);
-    case 2: return launch_gather<Src, 2>(rows, n, D, sh, out, status, stream);
-    default: return launch_gather<Src, 1>(rows, n, D, sh, out, status, stream);
+    case 16: return launch_gather<Src, 16>(rows, n, D, sh, out, order, status, stream);
+    case 8: return launch_gather<Src, 8>(rows, n, D, sh, out, order, status, stream);
+    case 4: return launch_gather<Src, 4>(rows, n, D, sh, out, order, status, stream);
+    case 2: return launch_gather<Src, 2>(rows, n, D, sh, out, order, status, stream);
+    default: return launch_gather<Src, 1>(rows, n, D, sh, out, order, status, stream);
   }
 }
 
 template <typename IdxT>
 int run_gather(int vec, const dgs_chunk_desc& d, const void* idx, int64_t n, int64_t D, int sh,
-               void* out, int32_t* status, cudaStream_t stream) {
+               void* out, const uint32_t* order, int32_t* status, cudaStream_t stream) {
   ChunkRows<IdxT> rows{d, static_cast<const IdxT*>(idx), D, d.total / D, sh};
-  return dispatch_vec(vec, rows, n, D, sh, out, status, stream);
+  return dispatch_vec(vec, rows, n, D, sh, out, order, status, stream);
 }
 
 // ---- cache table build -------------------------------------------------------
@@ -293,7 +310,7 @@ int run_cache_fetch(int vec, const dgs_chunk_desc& gpu, const void* cpu_data, in
                         gpu.total / D,
                         cpu_rows,
                         sh};
-  return dispatch_vec(vec, rows, n, D, sh, out, status, stream);
+  return dispatch_vec(vec, rows, n, D, sh, out, nullptr, status, stream);
 }
 
 // largest power of two <= 16 dividing x (x == 0 counts as "any")
@@ -343,8 +360,8 @@ int gather_vec_bytes(const dgs_chunk_desc& d, int64_t D, const void* out) {
 }  // namespace dgs
 
 extern "C" int dgs_gather_rows(const dgs_chunk_desc* t, int32_t location_class, const void* idx,
-                               int32_t ids64, int64_t n, int64_t D, void* out, int32_t* status,
-                               dgs_stream_t stream) {
+                               int32_t ids64, int64_t n, int64_t D, void* out, const uint32_t* order,
+                               int32_t* status, dgs_stream_t stream) {
   using namespace dgs;
   (void)location_class;  // hint only: the owner is resolved per row for every class
   int rc = validate_desc(t, "dgs_gather_rows");
@@ -356,8 +373,10 @@ extern "C" int dgs_gather_rows(const dgs_chunk_desc* t, int32_t location_class, 
   const int sh = esz_log2(t->esz);
   const int vec = gather_vec_bytes(*t, D, out);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return ids64 ? run_gather<int64_t>(vec, *t, idx, n, D, sh, out, status, s)
-               : run_gather<int32_t>(vec, *t, idx, n, D, sh, out, status, s);
+  DGS_REQUIRE(order == nullptr || n <= 0xFFFFFFFFll, DGS_ERR_UNSUPPORTED,
+              "dgs_gather_rows: a processing order covers at most 2^32 ids");
+  return ids64 ? run_gather<int64_t>(vec, *t, idx, n, D, sh, out, order, status, s)
+               : run_gather<int32_t>(vec, *t, idx, n, D, sh, out, order, status, s);
 }
 
 extern "C" int64_t dgs_cache_table_slots(int64_t n_keys) {

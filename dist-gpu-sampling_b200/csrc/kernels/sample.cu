@@ -183,8 +183,9 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
                       const int64_t n, const int64_t k, const bool replace,
                       const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
                       const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
-                      const uint64_t key, IdT* coo_row, IdT* coo_col, const int64_t out_capacity,
-                      int64_t* __restrict__ picked_pos, int32_t* __restrict__ status) {
+                      const uint32_t* __restrict__ order, const uint64_t key, IdT* coo_row, IdT* coo_col,
+                      const int64_t out_capacity, int64_t* __restrict__ picked_pos,
+                      int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
   constexpr int GROUPS = SAMPLE_BLOCK / G;  // seeds per CTA
   const int lane = threadIdx.x & 31;
@@ -195,8 +196,10 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
   const bool fast = !replace && k <= G;  // uniform over the grid
 
   {  // one seed per group; all 32 lanes of a warp walk through the same code
-    const int64_t i = static_cast<int64_t>(blockIdx.x) * GROUPS + group;
-    const bool valid = i < n;
+    const int64_t slot = static_cast<int64_t>(blockIdx.x) * GROUPS + group;
+    const bool valid = slot < n;
+    // which seed this group serves: the slot itself, or the slot's entry of the processing order
+    const int64_t i = (valid && order != nullptr) ? static_cast<int64_t>(order[slot]) : slot;
     const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, valid);
     const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
     const int64_t seed = valid ? static_cast<int64_t>(seeds[i]) : 0;
@@ -318,8 +321,9 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
                        const int64_t n, const int64_t k, const bool replace,
                        const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
                        const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
-                       const uint64_t key, IdT* coo_row, IdT* coo_col, const int64_t out_capacity,
-                       int64_t* __restrict__ picked_pos, int32_t* __restrict__ status) {
+                       const uint32_t* __restrict__ order, const uint64_t key, IdT* coo_row, IdT* coo_col,
+                       const int64_t out_capacity, int64_t* __restrict__ picked_pos,
+                       int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
   const int l = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -329,8 +333,9 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
   const float FLOOR_POS_W = -3.0e+38f;           // clamp for positive weights
 
   {  // one seed per warp
-    const int64_t i = static_cast<int64_t>(blockIdx.x) * WARPS + warp;
-    if (i >= n) return;  // warp-uniform
+    const int64_t slot = static_cast<int64_t>(blockIdx.x) * WARPS + warp;
+    if (slot >= n) return;  // warp-uniform
+    const int64_t i = order != nullptr ? static_cast<int64_t>(order[slot]) : slot;
     const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, true);
     const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
     const int64_t seed = static_cast<int64_t>(seeds[i]);
@@ -463,13 +468,14 @@ __global__ void zero_total_kernel(int64_t* nnz) { *nnz = 0; }
 
 template <typename IdT>
 int launch_uniform(const dgs_chunk_desc& indices, const void* seeds, int64_t n, int64_t k,
-                   bool replace, const PlanView& pv, uint64_t key, void* coo_row, void* coo_col,
+                   bool replace, const PlanView& pv, const uint32_t* order, uint64_t key, void* coo_row,
+                   void* coo_col,
                    int64_t cap, int64_t* pos, int32_t* status, cudaStream_t s) {
 #define DGS_LAUNCH_U(G)                                                                            \
   sample_uniform_kernel<IdT, G>                                                                    \
       <<<static_cast<unsigned>((n + SAMPLE_BLOCK / G - 1) / (SAMPLE_BLOCK / G)), SAMPLE_BLOCK, 0, s>>>( \
           indices, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off, \
-          pv.tile_off, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, status)
+          pv.tile_off, order, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, status)
   if (k <= 4) DGS_LAUNCH_U(4);
   else if (k <= 8) DGS_LAUNCH_U(8);
   else if (k <= 16) DGS_LAUNCH_U(16);
@@ -520,8 +526,8 @@ extern "C" int dgs_sample_plan(const dgs_chunk_desc* indptr, const void* seeds, 
 
 extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* seeds, int32_t ids64,
                                   int64_t n, int64_t k, int32_t replace, const void* plan,
-                                  uint64_t rng_seed, uint64_t rng_offset, void* coo_row,
-                                  void* coo_col, int64_t out_capacity, int64_t* nnz,
+                                  const uint32_t* order, uint64_t rng_seed, uint64_t rng_offset,
+                                  void* coo_row, void* coo_col, int64_t out_capacity, int64_t* nnz,
                                   int64_t* picked_pos, int32_t* status, dgs_stream_t stream) {
   using namespace dgs;
   int rc = validate_desc(indices, "dgs_sample_uniform");
@@ -542,9 +548,9 @@ extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* see
               "dgs_sample_uniform: null output");
   const PlanView pv = plan_view(const_cast<void*>(plan), n);
   const uint64_t key = mix64(rng_seed) ^ mix64(rng_offset ^ 0xA5A5A5A55A5A5A5Aull);
-  rc = ids64 ? launch_uniform<int64_t>(*indices, seeds, n, k, replace != 0, pv, key, coo_row, coo_col,
+  rc = ids64 ? launch_uniform<int64_t>(*indices, seeds, n, k, replace != 0, pv, order, key, coo_row, coo_col,
                                        out_capacity, picked_pos, status, s)
-             : launch_uniform<int32_t>(*indices, seeds, n, k, replace != 0, pv, key, coo_row, coo_col,
+             : launch_uniform<int32_t>(*indices, seeds, n, k, replace != 0, pv, order, key, coo_row, coo_col,
                                        out_capacity, picked_pos, status, s);
   if (rc != DGS_OK) return rc;
   if (nnz != nullptr) {
@@ -556,8 +562,8 @@ extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* see
 
 extern "C" int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chunk_desc* probs,
                                    const void* seeds, int32_t ids64, int64_t n, int64_t k,
-                                   int32_t replace, const void* plan, uint64_t rng_seed,
-                                   uint64_t rng_offset, void* coo_row, void* coo_col,
+                                   int32_t replace, const void* plan, const uint32_t* order,
+                                   uint64_t rng_seed, uint64_t rng_offset, void* coo_row, void* coo_col,
                                    int64_t out_capacity, int64_t* nnz, int64_t* picked_pos,
                                    int32_t* status, dgs_stream_t stream) {
   using namespace dgs;
@@ -589,12 +595,12 @@ extern "C" int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chun
   if (ids64)
     sample_weighted_kernel<int64_t><<<grid, SAMPLE_BLOCK, 0, s>>>(
         *indices, *probs, static_cast<const int64_t*>(seeds), n, k, replace != 0, pv.row_begin, pv.deg,
-        pv.local_off, pv.tile_off, key, static_cast<int64_t*>(coo_row), static_cast<int64_t*>(coo_col), out_capacity,
+        pv.local_off, pv.tile_off, order, key, static_cast<int64_t*>(coo_row), static_cast<int64_t*>(coo_col), out_capacity,
         picked_pos, status);
   else
     sample_weighted_kernel<int32_t><<<grid, SAMPLE_BLOCK, 0, s>>>(
         *indices, *probs, static_cast<const int32_t*>(seeds), n, k, replace != 0, pv.row_begin, pv.deg,
-        pv.local_off, pv.tile_off, key, static_cast<int32_t*>(coo_row), static_cast<int32_t*>(coo_col), out_capacity,
+        pv.local_off, pv.tile_off, order, key, static_cast<int32_t*>(coo_row), static_cast<int32_t*>(coo_col), out_capacity,
         picked_pos, status);
   DGS_LAUNCH_CHECK();
   if (nnz != nullptr) {

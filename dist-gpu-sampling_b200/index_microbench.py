@@ -34,6 +34,9 @@ def main():
     ap.add_argument("--ids", type=int, default=1_000_000, help="row ids per query")
     ap.add_argument("--host-frac", type=float, default=0.0, help="fraction of rows kept in the host tail")
     ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"])
+    ap.add_argument("--id-window", type=int, default=0,
+                    help="draw the ids from a window of this many rows at the start of the next rank's chunk "
+                         "(all remote, one peer, limited address range); 0 = whole table")
     ap.add_argument("--misalign", type=int, default=0, help="extra bytes of capacity: rows straddle chunks")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -62,7 +65,8 @@ def main():
     sub = table._CAPI_get_sub_device_tensor()
     each = sub.numel()
     step = 1 << 26
-    for lo in range(0, each, step):
+    nofill = os.environ.get("DGS_MB_NOFILL") == "1"   # bandwidth-only runs on uninitialised data
+    for lo in range(0, 0 if nofill else each, step):
         n = min(step, each - lo)
         sub[lo:lo + n] = synth.hashed_values(rank * each + lo, n, device=dev)
     host = table._CAPI_get_host_tensor()
@@ -77,7 +81,11 @@ def main():
 
     g = torch.Generator(device=dev)
     g.manual_seed(100 + rank)
-    if args.dist == "uniform":
+    if args.id_window > 0:
+        per_gpu = each // D
+        ids = torch.randint(0, min(args.id_window, per_gpu), (args.ids,), device=dev, generator=g) \
+            + ((rank + 1) % world) * per_gpu
+    elif args.dist == "uniform":
         ids = torch.randint(0, rows, (args.ids,), device=dev, generator=g)
     else:  # Zipf(1.1) ranks by inverse CDF, rank -> row through a fixed permutation
         u = torch.rand(args.ids, device=dev, generator=g, dtype=torch.float64)
@@ -130,8 +138,9 @@ def main():
              ("local_index", table._CAPI_local_index, lo_ids, hbm),
              ("remote_index", table._CAPI_remote_index, re_ids, 770.0),
              ("host_index", table._CAPI_host_index, ho_ids, host_link)]
+    solo = os.environ.get("DGS_MB_SOLO_RANK")       # only this rank issues requests, the others just serve
     for name, fn, idx, peak in cases:
-        if idx.numel() == 0:
+        if idx.numel() == 0 or (solo is not None and int(solo) != rank):
             continue
         out, ms = timed(fn, idx)
         payload = idx.numel() * D * 4

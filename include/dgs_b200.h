@@ -128,6 +128,21 @@ DGS_API int64_t dgs_alloc_current_bytes(void);
  * word (replaces the device asserts of src/cuda/*.cu).  `status` arguments
  * below are device-writable int32 words (pinned memory is fine) or NULL. */
 
+/* ---- locality order ------------------------------------------------------ */
+/* No counterpart in the reference.  order[0..n) becomes a permutation of
+ * 0..n-1 that lists the request's positions in coarse address order (counting
+ * sort on the high bits of the id; id_space = number of rows / nodes).  Passing
+ * it to dgs_gather_rows / dgs_sample_* makes them visit the ids in that order
+ * while writing every result where it belongs in the request: same output,
+ * far fewer distinct pages in flight.  Optional: it helps when address
+ * translation limits a request (mappings on small pages), and costs a few
+ * percent when it does not.
+ * scratch: dgs_locality_order_scratch_bytes() bytes. */
+DGS_API size_t dgs_locality_order_scratch_bytes(void);
+DGS_API int dgs_locality_order(const void* ids, int32_t ids64, int64_t n, int64_t id_space,
+                               uint32_t* order, void* scratch, size_t scratch_bytes,
+                               dgs_stream_t stream);
+
 /* ---- row gather -------------------------------------------------------- */
 enum { DGS_CLASS_ANY = 0, DGS_CLASS_LOCAL = 1, DGS_CLASS_REMOTE = 2, DGS_CLASS_HOST = 3 };
 /* IndexFromChunkTensorCUDA / Local.. / Remote.. / Host..,
@@ -135,10 +150,11 @@ enum { DGS_CLASS_ANY = 0, DGS_CLASS_LOCAL = 1, DGS_CLASS_REMOTE = 2, DGS_CLASS_H
  *   out[i*D + j] = T.At(idx[i]*D + j),  i < n, j < D.
  * `location_class` is a hint only (all classes resolve the owner per row, so
  * the result is the same for ids of any class).  A row id outside the tensor
- * yields a zero row and DGS_ERR_RANGE in *status. */
+ * yields a zero row and DGS_ERR_RANGE in *status.  `order` is NULL or a
+ * permutation from dgs_locality_order(idx, ...): processing order only. */
 DGS_API int dgs_gather_rows(const dgs_chunk_desc* t, int32_t location_class,
                     const void* idx, int32_t ids64, int64_t n, int64_t D,
-                    void* out, int32_t* status, dgs_stream_t stream);
+                    void* out, const uint32_t* order, int32_t* status, dgs_stream_t stream);
 
 /* SplitIndexFromChunkTensorCUDA, src/cuda/index_with_chunk_tensor.cu:55-108.
  * Stable 3-way partition of the ids: out = [local ids | remote ids | host ids]
@@ -197,10 +213,11 @@ DGS_API int dgs_sample_plan(const dgs_chunk_desc* indptr, const void* seeds, int
  * If picked_pos != NULL it receives, per output, the position inside the row
  * (int64) -- a test hook for multigraph validity checks.
  * Randomness: Philox4x32-10 keyed by `rng_seed`, counter from `rng_offset`
- * and the seed position; identical arguments give identical output. */
+ * and the seed position; identical arguments give identical output.
+ * `order` is NULL or a permutation from dgs_locality_order(seeds, ...). */
 DGS_API int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* seeds,
                        int32_t ids64, int64_t n_seeds, int64_t k, int32_t replace,
-                       const void* plan, uint64_t rng_seed, uint64_t rng_offset,
+                       const void* plan, const uint32_t* order, uint64_t rng_seed, uint64_t rng_offset,
                        void* coo_row, void* coo_col, int64_t out_capacity,
                        int64_t* nnz, int64_t* picked_pos, int32_t* status,
                        dgs_stream_t stream);
@@ -213,7 +230,7 @@ DGS_API int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* seeds,
  * With replacement: k draws proportional to max(w,0). */
 DGS_API int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chunk_desc* probs,
                         const void* seeds, int32_t ids64, int64_t n_seeds,
-                        int64_t k, int32_t replace, const void* plan,
+                        int64_t k, int32_t replace, const void* plan, const uint32_t* order,
                         uint64_t rng_seed, uint64_t rng_offset, void* coo_row,
                         void* coo_col, int64_t out_capacity, int64_t* nnz,
                         int64_t* picked_pos, int32_t* status, dgs_stream_t stream);
