@@ -1,7 +1,7 @@
 """Benchmark of the hot path: 3-hop neighbour sampling + relabel + feature gather.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload products|papers100m|small] [--batch 1024]
+                  [--workload products|papers100m|friendster|small] [--batch 1024] [--weighted] [--scale F]
 
 One step = one mini-batch per rank through the reference-facing operators:
   for fan_out in reversed([15, 10, 5]):  sample_neighbors_with_chunk_tensor -> tensor_relabel
@@ -11,7 +11,12 @@ power law, 100 fp32 features per node) whose indptr / indices / features live in
 ChunkTensors split evenly over the N GPUs of the node (weak scaling: every rank
 samples its own 1,024-seed batches).  `--workload papers100m` is the
 Papers100M-shaped configuration (111 M nodes, ~1.6 B edges, 128 features: 70 GB,
-which fits one B200 or is split over N).
+which fits one B200 or is split over N).  `--workload friendster` is the
+Friendster-shaped hybrid configuration: fan-out [10, 10], 256 features, node ids
+ranked by in-degree, 40 % of features and indices in the pinned host tail; it
+runs at a quarter of the node count by default (`--scale 1` for the full 65.6 M
+nodes / 3.6 B edges, which pins ~38 GB of host memory).  `--weighted` samples with
+per-edge weights.
 
 Printed JSON (rank 0, one line):
   value      sampled edges/s of the whole job, device-timed, seeds resident in HBM;
@@ -38,13 +43,29 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-FANOUTS = [15, 10, 5]
 WORKLOADS = {
-    # name: (nodes, mean degree, gamma, feature dim, train set size)
-    "products": (2_449_029, 50.5, 2.1, 100, 196_615),
-    "papers100m": (111_059_956, 14.5, 2.3, 128, 1_207_179),
-    "small": (100_000, 20.0, 2.1, 64, 20_000),
+    # nodes, mean degree, power-law exponent, feature width, training-set size, fan-outs,
+    # fraction of features/indices kept on the GPUs (the rest is the pinned host tail),
+    # node ids ranked by in-degree (hot rows first -> they land in the GPU chunks)
+    "products": dict(nodes=2_449_029, mean_deg=50.5, gamma=2.1, dim=100, train=196_615, fanouts=[15, 10, 5],
+                     gpu_frac=1.0, degree_sorted=False),
+    "papers100m": dict(nodes=111_059_956, mean_deg=14.5, gamma=2.3, dim=128, train=1_207_179,
+                       fanouts=[15, 10, 5], gpu_frac=1.0, degree_sorted=False),
+    "friendster": dict(nodes=65_608_366, mean_deg=55.0, gamma=2.2, dim=256, train=1_000_000, fanouts=[10, 10],
+                       gpu_frac=0.6, degree_sorted=True),
+    "small": dict(nodes=100_000, mean_deg=20.0, gamma=2.1, dim=64, train=20_000, fanouts=[15, 10, 5],
+                  gpu_frac=1.0, degree_sorted=False),
 }
+
+
+def workload(args):
+    """Workload parameters with --scale applied to the node count (edges follow: the mean degree is fixed)."""
+    w = dict(WORKLOADS[args.workload])
+    scale = args.scale if args.scale > 0 else (0.25 if args.workload == "friendster" else 1.0)
+    w["scale"] = scale
+    w["nodes"] = max(1000, int(w["nodes"] * scale))
+    w["train"] = max(args.batch, min(w["train"], w["nodes"] // 2))
+    return w
 # kernels of this library launched per operator call (memsets are not kernels)
 LAUNCHES_SAMPLE = 2   # plan (+ tile scan in its last CTA), sample
 LAUNCHES_RELABEL = 4  # insert, count (+ tile scan in its last CTA), number, lookup
@@ -62,6 +83,10 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="products", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=1024)
+    ap.add_argument("--scale", type=float, default=0.0,
+                    help="node-count factor; 0 = 1.0 (friendster: 0.25, so that the pinned tail stays ~10 GB)")
+    ap.add_argument("--weighted", action="store_true",
+                    help="sample with per-edge fp32 U(0,1) weights (the weighted operator) instead of uniformly")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -119,12 +144,18 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm), "samples_total": len(all_rows)}
 
 
-def build_graph(workload, device):
+def build_graph(w, device):
     """Same seeded graph on every rank (generated on `device`)."""
     synth = importlib.import_module("dist-gpu-sampling_b200.synth")
-    nodes, mean_deg, gamma, dim, train = WORKLOADS[workload]
-    indptr, indices = synth.chung_lu_csc(nodes, mean_deg, gamma, seed=11, device=device)
-    return indptr, indices, nodes, dim, train
+    indptr, indices = synth.chung_lu_csc(w["nodes"], w["mean_deg"], w["gamma"], seed=11, device=device,
+                                         degree_sorted=w["degree_sorted"])
+    return indptr, indices
+
+
+def edge_weights(start, count, device):
+    """Per-edge sampling weight in (0, 1] as a function of the edge index."""
+    synth = importlib.import_module("dist-gpu-sampling_b200.synth")
+    return synth.hashed_values(start, count, device=device, salt=17) * 0.5 + 0.5000001
 
 
 def feature_values(start, count, device):
@@ -144,14 +175,18 @@ def make_features(nodes, dim, device):
     return out.view(nodes, dim)
 
 
-def config_dict(args, n_edges_graph, world):
-    nodes, mean_deg, gamma, dim, train = WORKLOADS[args.workload]
-    return {"workload": "%s-shaped synthetic: %d nodes, %d edges (Chung-Lu gamma=%.1f), CSC int64, "
-                        "features [%d,%d] fp32" % (args.workload, nodes, n_edges_graph, gamma, nodes, dim),
-            "fanouts": FANOUTS, "batch_per_rank": args.batch, "global_batch": args.batch * world,
-            "train_set": train, "replace": False,
-            "step": "3 x (sample_neighbors_with_chunk_tensor + tensor_relabel) + features._CAPI_index(input_nodes)",
-            "storage": "indptr/indices/features in ChunkTensors split evenly over %d GPU(s), no host tail" % world,
+def config_dict(args, w, n_edges_graph, world):
+    nodes, dim = w["nodes"], w["dim"]
+    op = "sample_neighbors_with_probs_with_chunk_tensor" if args.weighted else "sample_neighbors_with_chunk_tensor"
+    tail = "no host tail" if w["gpu_frac"] >= 1.0 else \
+        "%.0f %% of features and indices in the pinned host tail, node ids ranked by in-degree" % (100 * (1 - w["gpu_frac"]))
+    return {"workload": "%s-shaped synthetic%s: %d nodes, %d edges (Chung-Lu gamma=%.1f), CSC int64, "
+                        "features [%d,%d] fp32" % (args.workload, "" if w["scale"] == 1.0 else " at scale %.2f" % w["scale"],
+                                                   nodes, n_edges_graph, w["gamma"], nodes, dim),
+            "fanouts": w["fanouts"], "batch_per_rank": args.batch, "global_batch": args.batch * world,
+            "train_set": w["train"], "replace": False, "weighted": bool(args.weighted),
+            "step": "%d x (%s + tensor_relabel) + features._CAPI_index(input_nodes)" % (len(w["fanouts"]), op),
+            "storage": "indptr/indices/features in ChunkTensors split evenly over %d GPU(s), %s" % (world, tail),
             "l2": "inputs larger than L2 (indices %.2f GB, features %.2f GB); a new seed batch every step"
                   % (n_edges_graph * 8 / 1e9, nodes * dim * 4 / 1e9)}
 
@@ -159,20 +194,20 @@ def config_dict(args, n_edges_graph, world):
 # ---------------------------------------------------------------------------
 # CPU arm (oracle port): used by --impl reference and by the cpu_baseline leg
 # ---------------------------------------------------------------------------
-def cpu_step(o, indptr, indices, feats, seeds):
-    frontier, blocks, edges = o.sample_blocks(indptr, indices, seeds, FANOUTS)
+def cpu_step(o, indptr, indices, feats, seeds, fanouts):
+    frontier, blocks, edges = o.sample_blocks(indptr, indices, seeds, fanouts)
     x = o.index_flat(feats, frontier)
     return edges, frontier.size, x
 
 
-def run_cpu(args, indptr, indices, feats, batches, steps, warmup, budget_s=None):
+def run_cpu(args, fanouts, indptr, indices, feats, batches, steps, warmup, budget_s=None):
     from oracle import oracle as o
     o.build()
     for b in range(warmup):
-        cpu_step(o, indptr, indices, feats, batches[b % len(batches)])
+        cpu_step(o, indptr, indices, feats, batches[b % len(batches)], fanouts)
     edges, t0, done = 0, time.perf_counter(), 0
     for b in range(steps):
-        e, _, _ = cpu_step(o, indptr, indices, feats, batches[(warmup + b) % len(batches)])
+        e, _, _ = cpu_step(o, indptr, indices, feats, batches[(warmup + b) % len(batches)], fanouts)
         edges += e
         done += 1
         if budget_s is not None and time.perf_counter() - t0 > budget_s:
@@ -188,16 +223,18 @@ def main_reference(args):
         return
     synth = importlib.import_module("dist-gpu-sampling_b200.synth")
     dev = "cuda" if torch.cuda.is_available() else "cpu"
-    indptr, indices, nodes, dim, train = build_graph(args.workload, dev)
+    w = workload(args)
+    nodes, dim, train = w["nodes"], w["dim"], w["train"]
+    indptr, indices = build_graph(w, dev)
     n_edges_graph = int(indices.numel())
     feats = make_features(nodes, dim, dev).cpu().numpy()
     indptr, indices = indptr.cpu().numpy(), indices.cpu().numpy()
     batches = synth.train_batches(nodes, train, args.batch)
-    value, ms, done, threads = run_cpu(args, indptr, indices, feats, batches, args.steps, args.warmup)
+    value, ms, done, threads = run_cpu(args, w["fanouts"], indptr, indices, feats, batches, args.steps, args.warmup)
     line = {"impl": "reference", "metric": "sampled_edges_per_s", "value": value, "unit": "edges/s",
             "n_gpus": args.gpus, "steps": done, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
-            "data": "synthetic", "config": config_dict(args, n_edges_graph, args.gpus),
+            "data": "synthetic", "config": config_dict(args, w, n_edges_graph, args.gpus),
             "cpu_baseline": {"value": value, "unit": "edges/s", "cores": threads, "kind": "port",
                              "sample": "%d batches of %d seeds (one per step), CPU restatement of the reference's "
                                        "sample->relabel loop + index_select, OpenMP over seeds" % (done, args.batch)},
@@ -231,35 +268,50 @@ def main_ours(args):
     ops = torch.ops.dgs_ops
 
     # ---- data: same graph on every rank, each rank keeps its own chunk ----
-    indptr, indices, nodes, dim, train = build_graph(args.workload, dev)
+    w = workload(args)
+    nodes, dim, train, fanouts = w["nodes"], w["dim"], w["train"], w["fanouts"]
+    indptr, indices = build_graph(w, dev)
     n_edges_graph = int(indices.numel())
+    fill = 1 << 26
 
-    def chunk_capacity(nbytes):
-        cap = -(-nbytes // world)
+    def chunk_capacity(nbytes, frac=1.0):
+        cap = -(-int(nbytes * frac) // world)
         return -(-cap // 16) * 16
 
-    def to_chunk(t):
-        ct = torch.classes.dgs_classes.ChunkTensor(list(t.shape), t.dtype,
-                                                   chunk_capacity(t.numel() * t.element_size()))
+    def fill_chunk(ct, total, values):
+        """values(start, count) -> device tensor of the flat elements [start, start+count)."""
         sub = ct._CAPI_get_sub_device_tensor()
-        flat = t.reshape(-1)
-        lo = rank * sub.numel()
-        n = max(0, min(sub.numel(), flat.numel() - lo))
-        if n > 0:
-            sub[:n].copy_(flat[lo:lo + n])
+        lo0 = rank * sub.numel()
+        for lo in range(0, max(0, min(sub.numel(), total - lo0)), fill):
+            n = min(fill, sub.numel() - lo, total - lo0 - lo)
+            sub[lo:lo + n] = values(lo0 + lo, n)
+        host = ct._CAPI_get_host_tensor()
+        if rank == 0 and host.numel():           # the pinned tail is shared: one rank writes it
+            thr = total - host.numel()
+            for lo in range(0, host.numel(), fill):
+                n = min(fill, host.numel() - lo)
+                host[lo:lo + n].copy_(values(thr + lo, n))
         return ct
 
-    c_indptr, c_indices = to_chunk(indptr), to_chunk(indices)
+    def to_chunk(t, frac=1.0):
+        flat = t.reshape(-1)
+        ct = torch.classes.dgs_classes.ChunkTensor(list(t.shape), t.dtype,
+                                                   chunk_capacity(flat.numel() * t.element_size(), frac))
+        return fill_chunk(ct, flat.numel(), lambda start, count: flat[start:start + count])
+
+    c_indptr = to_chunk(indptr)
+    c_indices = to_chunk(indices, w["gpu_frac"])
+    c_probs = None
+    if args.weighted:
+        c_probs = torch.classes.dgs_classes.ChunkTensor([n_edges_graph], torch.float32, chunk_capacity(n_edges_graph * 4))
+        fill_chunk(c_probs, n_edges_graph, lambda start, count: edge_weights(start, count, dev))
     # features: every rank fills its own chunk in place
-    c_feats = torch.classes.dgs_classes.ChunkTensor([nodes, dim], torch.float32, chunk_capacity(nodes * dim * 4))
-    sub = c_feats._CAPI_get_sub_device_tensor()
-    fill = 1 << 26
-    for lo in range(0, min(sub.numel(), max(0, nodes * dim - rank * sub.numel())), fill):
-        n = min(fill, sub.numel() - lo, nodes * dim - rank * sub.numel() - lo)
-        sub[lo:lo + n] = feature_values(rank * sub.numel() + lo, n, dev)
-    del sub
+    c_feats = torch.classes.dgs_classes.ChunkTensor([nodes, dim], torch.float32,
+                                                    chunk_capacity(nodes * dim * 4, w["gpu_frac"]))
+    fill_chunk(c_feats, nodes * dim, lambda start, count: feature_values(start, count, dev))
     host_graph = None
-    if rank == 0 and not args.no_cpu_baseline and world == 1 and args.workload != "papers100m":
+    if rank == 0 and not args.no_cpu_baseline and world == 1 and args.workload in ("products", "small") \
+            and not args.weighted:
         host_graph = (indptr.cpu().numpy(), indices.cpu().numpy(), make_features(nodes, dim, dev).cpu().numpy())
     del indptr, indices
     torch.cuda.empty_cache()
@@ -274,7 +326,7 @@ def main_ours(args):
     torch.manual_seed(1234 + rank)
 
     def step(seeds):
-        frontier, blocks, n_edges = pkg.sample_blocks(seeds, FANOUTS, c_indptr, c_indices)
+        frontier, blocks, n_edges = pkg.sample_blocks(seeds, fanouts, c_indptr, c_indices, probs=c_probs)
         return frontier, n_edges
 
     def barrier():
@@ -326,7 +378,7 @@ def main_ours(args):
         x = c_feats._CAPI_index(fr)
         chk = torch.stack([x.sum(), fr.sum().to(torch.float32)]).cpu()   # the step's result leaves the device
         e2e_edges += e
-        d2h = chk.numel() * 4 + 8 * (2 * len(FANOUTS))                    # + the sizes every operator reads back
+        d2h = chk.numel() * 4 + 8 * (2 * len(fanouts))                    # + the sizes every operator reads back
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
@@ -352,7 +404,7 @@ def main_ours(args):
             "metric": "sampled_edges_per_s", "value": edges_all / (total_ms * 1e-3), "unit": "edges/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
-            "data": "synthetic", "config": config_dict(args, n_edges_graph, world),
+            "data": "synthetic", "config": config_dict(args, w, n_edges_graph, world),
             "breakdown": {"sample_relabel_ms_per_step": sample_ms / args.steps,
                           "gather_ms_per_step": gather_ms / args.steps,
                           "sampling_only_edges_per_s": edges_all / (sample_ms * 1e-3),
@@ -361,7 +413,7 @@ def main_ours(args):
                           "gather_payload_gbs_all_ranks": rows_all * dim * 4 / (gather_ms * 1e-3) / 1e9},
             "e2e": {"value": e2e_edges_all / (e2e_ms * 1e-3), "unit": "edges/s",
                     "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * (len(FANOUTS) * (LAUNCHES_SAMPLE + LAUNCHES_RELABEL) + LAUNCHES_GATHER),
+            "gpu_launches": args.steps * (len(fanouts) * (LAUNCHES_SAMPLE + LAUNCHES_RELABEL) + LAUNCHES_GATHER),
             "roofline": {"kernel": "gather_rows_kernel (features._CAPI_index)", "bound": "hbm",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind,
@@ -371,7 +423,7 @@ def main_ours(args):
             "clocks": clock_info,
         }
         if host_graph is not None:
-            v, ms, done, threads = run_cpu(args, host_graph[0], host_graph[1], host_graph[2], batches_np,
+            v, ms, done, threads = run_cpu(args, fanouts, host_graph[0], host_graph[1], host_graph[2], batches_np,
                                            steps=10 ** 6, warmup=1, budget_s=args.cpu_seconds)
             line["cpu_baseline"] = {"value": v, "unit": "edges/s", "cores": threads, "kind": "port",
                                     "sample": "%d batches of %d seeds in %.1f s (same graph and step)"
@@ -379,7 +431,7 @@ def main_ours(args):
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)
-    del c_indptr, c_indices, c_feats     # collective teardown, same order on every rank
+    del c_indptr, c_indices, c_feats, c_probs     # collective teardown, same order on every rank
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

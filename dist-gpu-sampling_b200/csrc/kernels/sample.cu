@@ -29,7 +29,9 @@
 //   * weighted sampling without replacement keeps the top-k keys in a sorted
 //     per-warp register list (lane i = i-th largest) with ballot-gated
 //     insertion; keys are compared in the log domain, log(u)/w, which orders
-//     exactly like u^(1/w) but does not underflow for small weights.
+//     exactly like u^(1/w) but does not underflow for small weights.  Rows
+//     are read in 512-edge windows (16 loads in flight per lane) and rows longer
+//     than 4096 edges are shared by the eight warps of the CTA and merged.
 //   * weighted sampling with replacement builds no cumulative array in global
 //     memory: the row is streamed twice through a warp scan and each draw is
 //     resolved by a ballot in the 32-edge window it falls into.
@@ -303,7 +305,8 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
 }
 
 // ---------------------------------------------------------------------------
-// weighted sampling: one warp per seed
+// weighted sampling: one warp per seed; rows longer than HUB_DEG edges are then
+// taken on by all eight warps of the CTA together
 // ---------------------------------------------------------------------------
 struct RowWeights {
   const dgs_chunk_desc& probs;
@@ -313,6 +316,82 @@ struct RowWeights {
     return direct != nullptr ? direct[e] : load_at<float>(probs, 2, rb + e);
   }
 };
+
+constexpr int64_t HUB_DEG = 4096;   // rows above this are scanned by the whole CTA
+constexpr int ARES_QUADS = 4;       // Philox blocks per lane and 512-edge window
+
+// The running top-k of one warp: lane j holds the j-th largest key and its
+// position in the row; `thresh` is the key held by lane k-1 (the entry bar).
+struct TopK {
+  float key;
+  int64_t pos;
+  float thresh;
+  __device__ __forceinline__ void insert(float nk, int64_t np, int l, int k) {
+    // warp-uniform call with nk > thresh; the keys >= nk form a prefix of the lanes
+    const int p = __popc(__ballot_sync(FULL_MASK, key >= nk));  // p <= k-1
+    const float up_key = __shfl_up_sync(FULL_MASK, key, 1);
+    const int64_t up_pos = __shfl_up_sync(FULL_MASK, pos, 1);
+    if (l > p) {
+      key = up_key;
+      pos = up_pos;
+    } else if (l == p) {
+      key = nk;
+      pos = np;
+    }
+    thresh = __shfl_sync(FULL_MASK, key, k - 1);
+  }
+};
+
+// A-Res over one window of 512 edges starting at `base`: key = log(u)/w, which
+// orders like u^(1/w).  The 16 weights a lane needs are loaded together (2 KB in
+// flight per warp); the uniforms come from one Philox block per four edges,
+// addressed by (seed position, edge index) so that the result does not depend on
+// which warp scans the window.
+__device__ __forceinline__ void ares_window(TopK& top, const RowWeights& W, int64_t base, int64_t deg,
+                                            uint64_t key, uint32_t i_lo, uint32_t i_hi, int l, int k) {
+  const float NEG_INF = __int_as_float(0xff800000);
+  const float FLOOR_ZERO_W = -3.402823466e+38f;  // weight <= 0: behind every positive weight
+  const float FLOOR_POS_W = -3.0e+38f;           // clamp for positive weights
+  float wv[4 * ARES_QUADS];
+#pragma unroll
+  for (int j = 0; j < 4 * ARES_QUADS; ++j) {
+    const int64_t e = base + j * 32 + l;
+    wv[j] = (e < deg) ? W(e) : 0.f;
+  }
+#pragma unroll
+  for (int q = 0; q < ARES_QUADS; ++q) {
+    if (base + q * 128 >= deg) break;  // warp-uniform
+    const uint64_t ctr = static_cast<uint64_t>((base >> 2) + q * 32) + static_cast<uint64_t>(l);
+    const Philox4 r = philox4x32_10(key ^ (static_cast<uint64_t>(TAG_ARES) << 32), i_lo, i_hi,
+                                    static_cast<uint32_t>(ctr), static_cast<uint32_t>(ctr >> 32));
+    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t e0 = base + (q * 4 + j) * 32;  // first edge of this group of 32
+      const float w = wv[q * 4 + j];
+      float ck = NEG_INF;
+      if (e0 + l < deg)
+        ck = (w > 0.f) ? fmaxf(__fdividef(__logf(unit_float(rw[j])), w), FLOOR_POS_W) : FLOOR_ZERO_W;
+      unsigned cand = __ballot_sync(FULL_MASK, ck > top.thresh);
+      while (cand) {
+        const int src = __ffs(cand) - 1;
+        cand &= cand - 1;
+        const float nk = __shfl_sync(FULL_MASK, ck, src);
+        if (nk > top.thresh) top.insert(nk, e0 + src, l, k);  // the bar may have risen since the ballot
+      }
+    }
+  }
+}
+
+// One warp's share of a row: windows base0, base0 + stride, ...
+// (The exponential-jump form of the sampler -- keys only for the edges that enter, a
+// streamed prefix sum for the rest -- was built and measured here: with fan-outs of
+// 10-32 and rows of 10^3-10^4 edges an entry costs ~250 instructions at a rate of k/n
+// per edge, and the kernel ran 1.6-2.3x slower than with per-edge keys, so it is not used.)
+__device__ __forceinline__ void ares_scan(TopK& top, const RowWeights& W, int64_t base0, int64_t stride,
+                                          int64_t deg, uint64_t key, uint32_t i_lo, uint32_t i_hi, int l, int k) {
+  for (int64_t base = base0; base < deg; base += stride) ares_window(top, W, base, deg, key, i_lo, i_hi, l, k);
+}
 
 template <typename IdT>
 __global__ void __launch_bounds__(SAMPLE_BLOCK)
@@ -329,77 +408,44 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
   const int warp = threadIdx.x >> 5;
   constexpr int WARPS = SAMPLE_BLOCK / 32;
   const float NEG_INF = __int_as_float(0xff800000);
-  const float FLOOR_ZERO_W = -3.402823466e+38f;  // weight <= 0: behind every positive weight
-  const float FLOOR_POS_W = -3.0e+38f;           // clamp for positive weights
+  __shared__ int s_hub[WARPS];  // warps whose seed is left to the whole CTA
+  __shared__ int s_nhub;
+  __shared__ float s_mkey[WARPS][32];
+  __shared__ int64_t s_mpos[WARPS][32];
+  if (threadIdx.x == 0) s_nhub = 0;
+  __syncthreads();
 
-  {  // one seed per warp
+  // ---- phase 1: one seed per warp ----
+  do {
     const int64_t slot = static_cast<int64_t>(blockIdx.x) * WARPS + warp;
-    if (slot >= n) return;  // warp-uniform
+    if (slot >= n) break;  // warp-uniform
     const int64_t i = order != nullptr ? static_cast<int64_t>(order[slot]) : slot;
     const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, true);
     const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
     const int64_t seed = static_cast<int64_t>(seeds[i]);
     const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
-    if (deg <= 0) return;
+    if (deg <= 0) break;
 
     if (!replace && deg <= k) {
       for (int64_t t = l; t < deg; t += 32) emit(o, t, seed, rb, t);
-      return;
+      break;
     }
     if (rb + deg > probs.total) {
       if (l == 0) raise_status(status, DGS_ERR_RANGE);
-      return;
+      break;
+    }
+    if (!replace && deg > HUB_DEG) {
+      if (l == 0) s_hub[atomicAdd(&s_nhub, 1)] = warp;
+      break;
     }
     int64_t run;
     const char* wp = resolve(probs, 2, rb, &run);
     const RowWeights W{probs, run >= deg ? reinterpret_cast<const float*>(wp) : nullptr, rb};
 
     if (!replace) {
-      // ---- A-Res: keep the k largest log(u)/w; lane j holds the j-th largest ----
-      float top_key = NEG_INF;
-      int64_t top_pos = -1;
-      float thresh = NEG_INF;  // key held by lane k-1
-      for (int64_t base = 0; base < deg; base += 128) {
-        // one Philox block per lane covers the lane's four edges of this window
-        const uint64_t ctr = static_cast<uint64_t>(base >> 2) + static_cast<uint64_t>(l);
-        const Philox4 r = philox4x32_10(key ^ (static_cast<uint64_t>(TAG_ARES) << 32), i_lo, i_hi,
-                                        static_cast<uint32_t>(ctr), static_cast<uint32_t>(ctr >> 32));
-        const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
-        float ck[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int64_t e = base + j * 32 + l;
-          ck[j] = NEG_INF;
-          if (e < deg) {
-            const float w = W(e);
-            ck[j] = (w > 0.f) ? fmaxf(__logf(unit_float(rw[j])) / w, FLOOR_POS_W) : FLOOR_ZERO_W;
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          unsigned cand = __ballot_sync(FULL_MASK, ck[j] > thresh);
-          while (cand) {
-            const int src = __ffs(cand) - 1;
-            cand &= cand - 1;
-            const float nk = __shfl_sync(FULL_MASK, ck[j], src);
-            if (nk > thresh) {  // thresh may have risen since the ballot; uniform over the warp
-              const int64_t np = base + j * 32 + src;
-              const int p = __popc(__ballot_sync(FULL_MASK, top_key >= nk));  // p <= k-1
-              const float up_key = __shfl_up_sync(FULL_MASK, top_key, 1);
-              const int64_t up_pos = __shfl_up_sync(FULL_MASK, top_pos, 1);
-              if (l > p) {
-                top_key = up_key;
-                top_pos = up_pos;
-              } else if (l == p) {
-                top_key = nk;
-                top_pos = np;
-              }
-              thresh = __shfl_sync(FULL_MASK, top_key, static_cast<int>(k) - 1);
-            }
-          }
-        }
-      }
-      if (l < k) emit(o, l, seed, rb, top_pos);
+      TopK top{NEG_INF, -1, NEG_INF};
+      ares_scan(top, W, 0, 128 * ARES_QUADS, deg, key, i_lo, i_hi, l, static_cast<int>(k));
+      if (l < k) emit(o, l, seed, rb, top.pos);
     } else {
       // ---- proportional draws: stream the row twice through a warp scan ----
       float total = 0.f;
@@ -449,6 +495,36 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
         if (mine) emit(o, t, seed, rb, pos);
       }
     }
+  } while (false);
+
+  // ---- phase 2: hub rows, all warps of the CTA on one row at a time ----
+  __syncthreads();
+  const int nhub = s_nhub;
+  for (int h = 0; h < nhub; ++h) {
+    const int64_t slot = static_cast<int64_t>(blockIdx.x) * WARPS + s_hub[h];
+    const int64_t i = order != nullptr ? static_cast<int64_t>(order[slot]) : slot;
+    const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, true);
+    const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
+    const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
+    int64_t run;
+    const char* wp = resolve(probs, 2, rb, &run);
+    const RowWeights W{probs, run >= deg ? reinterpret_cast<const float*>(wp) : nullptr, rb};
+    TopK top{NEG_INF, -1, NEG_INF};
+    ares_scan(top, W, static_cast<int64_t>(warp) * 128 * ARES_QUADS, 128 * ARES_QUADS * WARPS, deg, key, i_lo,
+              i_hi, l, static_cast<int>(k));
+    s_mkey[warp][l] = top.key;
+    s_mpos[warp][l] = top.pos;
+    __syncthreads();
+    if (warp == 0) {  // merge the other warps' lists into this one; every list is sorted, so stop at the bar
+      for (int ww = 1; ww < WARPS; ++ww)
+        for (int t = 0; t < k; ++t) {
+          const float nk = s_mkey[ww][t];  // same address for all lanes: broadcast
+          if (!(nk > top.thresh)) break;
+          top.insert(nk, s_mpos[ww][t], l, static_cast<int>(k));
+        }
+      if (l < k) emit(o, l, static_cast<int64_t>(seeds[i]), rb, top.pos);
+    }
+    __syncthreads();
   }
 }
 

@@ -27,13 +27,17 @@ def distinct_seeds(num_nodes, n, seed=2):
     return rng.choice(num_nodes, size=n, replace=False).astype(np.int64)
 
 
-def chung_lu_csc(num_nodes, mean_degree, gamma, seed, device="cpu", max_degree=None, chunk=1 << 25):
+def chung_lu_csc(num_nodes, mean_degree, gamma, seed, device="cpu", max_degree=None, chunk=1 << 25,
+                 degree_sorted=False):
     """Chung-Lu style power-law graph built directly in CSC with torch ops.
 
     Node v gets expected degree w_v proportional to (r_v + i0)^(-1/(gamma-1)) where
     r is a random permutation (degree independent of id), scaled to the requested
     mean; its in-degree is Poisson(w_v) and every neighbour is drawn with
-    probability proportional to w.  Returns (indptr, indices) int64 tensors on `device`.
+    probability proportional to w.  With degree_sorted the permutation is the
+    identity: node ids are ranked by expected in-degree, hottest first (the
+    renumbering a cache-by-degree placement wants).
+    Returns (indptr, indices) int64 tensors on `device`.
     """
     import torch
     g = torch.Generator(device=device)
@@ -41,7 +45,10 @@ def chung_lu_csc(num_nodes, mean_degree, gamma, seed, device="cpu", max_degree=N
     if max_degree is None:
         max_degree = max(16.0, num_nodes ** 0.5 * mean_degree ** 0.5)
     alpha = 1.0 / (gamma - 1.0)
-    rank = torch.randperm(num_nodes, generator=g, device=device).to(torch.float64)
+    if degree_sorted:
+        rank = torch.arange(num_nodes, device=device, dtype=torch.float64)
+    else:
+        rank = torch.randperm(num_nodes, generator=g, device=device).to(torch.float64)
     # i0 bounds the largest expected degree: w_max / w_mean ~ ((N+i0)/i0)^alpha
     i0 = 1.0
     for _ in range(60):

@@ -233,6 +233,69 @@ def test_weighted_without_replacement_matches_ares(words, deg, k):
     assert np.abs(z).max() < stats.norm.isf(0.01 / (2 * deg))
 
 
+@pytest.mark.parametrize("deg,k", [(1500, 1), (3000, 8), (700, 32), (9000, 5)])
+def test_weighted_long_rows(words, deg, k):
+    """Rows longer than one 512-edge window (and above 4096 edges: scanned by a whole CTA).
+    With equal weights every position must be
+    included with probability k/deg wherever it lies in the row; with k = 1 the pick must be
+    exactly proportional to the weights."""
+    from gpu_util import plain_desc, sample
+    trials = 300_000 // max(1, k // 4)
+    ip, ix = to_dev(np.array([0, deg])), to_dev(np.arange(deg))
+    sd = torch.zeros(trials, dtype=torch.int64, device="cuda")
+    rng = np.random.default_rng(deg)
+    if k == 1:
+        w = (rng.random(deg) + 0.05).astype(np.float32)
+        w[rng.random(deg) < 0.2] = 0.0
+    else:
+        w = np.full(deg, 0.37, dtype=np.float32)
+    pr = torch.from_numpy(w).cuda()
+    _, _, pos = sample(plain_desc(ip), plain_desc(ix), sd, k, False, words, probs_desc=plain_desc(pr), rng=(11, deg))
+    assert words.take_status() == 0
+    per_row = np.sort(pos.reshape(trials, k), axis=1)
+    assert (np.diff(per_row, axis=1) > 0).all() if k > 1 else True
+    nb = 50
+    edges = np.linspace(0, deg, nb + 1).astype(int)
+    counts = np.histogram(pos, bins=edges)[0]
+    expect = np.add.reduceat(w.astype(np.float64), edges[:-1])
+    expect = expect / expect.sum() * counts.sum()
+    if k == 1:
+        assert (w[pos] > 0).all()
+        assert stats.chisquare(counts, expect).pvalue > 0.01
+    else:
+        # inclusion counts of buckets are slightly negatively correlated: the statistic is conservative
+        assert stats.chisquare(counts, expect).pvalue > 0.01
+
+
+def test_weighted_hub_rows(oracle, words):
+    """Rows longer than 4096 edges are scanned by a whole CTA: same contract (valid, distinct
+    positions) and picks proportional to the weights."""
+    from gpu_util import plain_desc, sample
+    deg, k, trials = 10_000, 4, 20_000
+    w = np.ones(deg, dtype=np.float32)
+    heavy = np.arange(deg) % 10 == 3
+    w[heavy] = 5.0
+    indptr = np.array([0, 3, 3 + deg, 3 + deg + 5000])          # a short row, the hub, a second hub
+    indices = np.arange(indptr[-1]) % 977
+    probs = np.concatenate([np.ones(3, np.float32), w, np.ones(5000, np.float32)])
+    ip, ix = to_dev(indptr), to_dev(indices)
+    pr = torch.from_numpy(probs).cuda()
+    seeds = np.ones(trials, dtype=np.int64)
+    seeds[::7] = 0
+    seeds[3::11] = 2
+    row, col, pos = sample(plain_desc(ip), plain_desc(ix), to_dev(seeds), k, False, words, probs_desc=plain_desc(pr))
+    assert words.take_status() == 0
+    oracle.check_sample(indptr, indices, seeds, k, False, row, col, pos)
+    hub = pos[row == 1]
+    n_draws = hub.size
+    share = heavy[hub].mean()
+    # with k << deg, without-replacement picks are proportional to the weights to first order
+    expect = 5.0 * heavy.sum() / (5.0 * heavy.sum() + (~heavy).sum())
+    assert abs(share - expect) < 4 * np.sqrt(expect * (1 - expect) / n_draws) + 2e-3
+    counts = np.bincount(hub // 1000, minlength=10)              # every part of the row is reached
+    assert stats.chisquare(counts).pvalue > 0.001
+
+
 def test_weighted_zero_weights_fill_only_leftovers(words):
     from gpu_util import plain_desc, sample
     deg, k = 40, 6
