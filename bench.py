@@ -401,6 +401,7 @@ def main_ours(args):
         achieved = rows_per_launch * row_alg_bytes / (gather_ms_launch * 1e-3) / 1e9
         per_row = NCU_TRAFFIC_BYTES_PER_ROW.get(dim)
         line = {
+            "library": os.environ.get("DGS_OPS_LIBRARY") or "dist-gpu-sampling_b200/lib/libdgs.so",
             "metric": "sampled_edges_per_s", "value": edges_all / (total_ms * 1e-3), "unit": "edges/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64",

@@ -42,14 +42,20 @@ def load_ops():
     makes with its libdgs.so (example/dgs_create_communicator.py:4)."""
     if not _loaded["ops"]:
         import torch
-        path = binding_path()
+        # DGS_OPS_LIBRARY points the same calls at another build of the operator library -- e.g. the
+        # reference's own kernels compiled for this GPU (oracle/build_reference.sh) for a side-by-side run
+        path = os.environ.get("DGS_OPS_LIBRARY") or binding_path()
         if not os.path.exists(path):
             raise RuntimeError(
                 "dgs-b200: %s is missing; run `python __graft_entry__.py` (or build.py) first. "
                 "There is no fallback path." % path)
         torch.ops.load_library(path)
         _loaded["ops"] = True
-    return binding_path()
+        if os.environ.get("DGS_OPS_LIBRARY") and not (torch.distributed.is_available()
+                                                      and torch.distributed.is_initialized()):
+            # the reference's ChunkTensor constructor reads the communicator's size: give it a group of one
+            torch.ops.dgs_ops._CAPI_set_nccl(1, torch.ops.dgs_ops._CAPI_get_unique_id(), 0)
+    return os.environ.get("DGS_OPS_LIBRARY") or binding_path()
 
 
 # ---------------------------------------------------------------------------

@@ -10,10 +10,14 @@
  * it cites.  Parity status:
  *   - placement / host-tail layout: pinned by the reference's only golden
  *     vector, the demo output in README.md:48-63 (example/demo.py:24-36).
- *   - index, split-index, relabel, sampling: the reference holds no test,
- *     fixture or golden vector for them and its CPU comparison point (DGL,
- *     unpinned version, README.md:23-24) is not available => PARITY UNPINNED
- *     beyond what follows mechanically from the cited lines.
+ *   - index, split-index, local/host index, relabel (int64 and int32, absent
+ *     ids), sampling of rows with deg <= fan-out, per-seed grouping with and
+ *     without replacement, cache fetch: pinned by outputs of the reference's
+ *     own kernels, compiled for sm_100a (oracle/build_reference.sh) and run on
+ *     a B200 (tests/golden/make_reference_golden.py ->
+ *     tests/golden/reference_b200.json; checked by tests/test_reference_golden.py).
+ *   - rows with deg > fan-out are stochastic in the reference (and re-seeded
+ *     with a constant there): compared by validity and distribution only.
  *
  * Ids are int64 throughout (int32 callers widen).  Build: see oracle/Makefile.
  */

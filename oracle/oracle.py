@@ -5,8 +5,9 @@ CPU-baseline leg of bench.py -- never by the product package.
 
 Every function restates the reference operator named in its docstring
 (paths are inside gpzlx1/Dist-GPU-sampling).  Parity status is stated in the
-header of dgs_oracle.c: placement is pinned by the README demo vector, the
-rest is "parity unpinned" (the reference ships no tests or CPU path).
+header of dgs_oracle.c: placement is pinned by the README demo vector, every
+deterministic operator output by vectors recorded from the reference's own
+kernels on a B200 (tests/golden/reference_b200.json).
 """
 import ctypes
 import os
