@@ -349,6 +349,7 @@ def main_ours(args):
     t_begin = torch.cuda.Event(enable_timing=True)
     t_end = torch.cuda.Event(enable_timing=True)
     edges = rows = 0
+    kept = []
     t_begin.record()
     for s in range(args.steps):
         seeds = dev_batches[my[(args.warmup + s) % len(my)]]
@@ -359,6 +360,8 @@ def main_ours(args):
         ev[s][2].record()
         edges += e
         rows += fr.numel()
+        if s >= args.steps - 8:
+            kept.append(fr)                      # frontiers for the kernel-timing pass below
     t_end.record()
     barrier()
     n_after = len(clocks.rows)
@@ -384,6 +387,24 @@ def main_ours(args):
     e2e_ms = e0.elapsed_time(e1)
     clock_info = clocks.stop(n_before, n_after) if rank == 0 else None
 
+    # ---- the gather kernel on its own: back-to-back launches over the last frontiers, so that the events
+    # bracket the kernel and not the host's launch gap (inside a step the host is still busy returning
+    # from the relabel operator when the GPU reaches the gather) ----
+    barrier()
+    n_k = max(16, min(args.steps, 64))
+    kev = [torch.cuda.Event(enable_timing=True) for _ in range(n_k + 1)]
+    for i in range(3):
+        c_feats._CAPI_index(kept[i % len(kept)])
+    kev[0].record()
+    k_rows = 0
+    for i in range(n_k):
+        c_feats._CAPI_index(kept[i % len(kept)])
+        kev[i + 1].record()
+        k_rows += kept[i % len(kept)].numel()
+    torch.cuda.synchronize()
+    k_ms = sum(kev[i].elapsed_time(kev[i + 1]) for i in range(n_k))
+    del kept
+
     # ---- reduce over ranks: max time, summed work ----
     stats = torch.tensor([total_ms, sample_ms, gather_ms, e2e_ms], dtype=torch.float64, device=dev)
     work = torch.tensor([edges, rows, e2e_edges], dtype=torch.float64, device=dev)
@@ -396,9 +417,10 @@ def main_ours(args):
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         row_alg_bytes = 8 + 2 * dim * 4
-        rows_per_launch = rows / args.steps
-        gather_ms_launch = gather_ms / args.steps
+        rows_per_launch = k_rows / n_k
+        gather_ms_launch = k_ms / n_k
         achieved = rows_per_launch * row_alg_bytes / (gather_ms_launch * 1e-3) / 1e9
+        in_step = (rows / args.steps) * row_alg_bytes / (gather_ms / args.steps * 1e-3) / 1e9
         per_row = NCU_TRAFFIC_BYTES_PER_ROW.get(dim)
         line = {
             "library": os.environ.get("DGS_OPS_LIBRARY") or "dist-gpu-sampling_b200/lib/libdgs.so",
@@ -410,7 +432,7 @@ def main_ours(args):
                           "gather_ms_per_step": gather_ms / args.steps,
                           "sampling_only_edges_per_s": edges_all / (sample_ms * 1e-3),
                           "edges_per_step_per_rank": edges / args.steps,
-                          "input_nodes_per_step_per_rank": rows_per_launch,
+                          "input_nodes_per_step_per_rank": rows / args.steps,
                           "gather_payload_gbs_all_ranks": rows_all * dim * 4 / (gather_ms * 1e-3) / 1e9},
             "e2e": {"value": e2e_edges_all / (e2e_ms * 1e-3), "unit": "edges/s",
                     "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": d2h},
@@ -420,6 +442,10 @@ def main_ours(args):
                          "peak_kind": peak_kind,
                          "algorithmic_bytes_per_row": row_alg_bytes,
                          "rows_per_launch": rows_per_launch, "ms_per_launch": gather_ms_launch,
+                         "launches_timed": n_k,
+                         "timing": "CUDA events around %d back-to-back launches on the frontiers of the last "
+                                   "timed steps (rank 0)" % n_k,
+                         "frac_inside_step": in_step / peak,
                          "traffic": per_row * rows_per_launch if per_row else None},
             "clocks": clock_info,
         }
