@@ -44,6 +44,7 @@ struct dgs_store {
   void* host = nullptr;         // host address of the tail
   void* host_dev = nullptr;     // device-visible address of the tail
   bool host_registered = false;
+  size_t host_reg_piece = 0;    // 0: one registration for the whole tail, else registered in pieces of this size
   bool host_is_shm = false;
   size_t host_bytes = 0;
   size_t local_bytes = 0;
@@ -84,7 +85,14 @@ struct Meta {
 // by destroy after its barriers).
 void release_local(dgs_store* s) {
   if (s->host != nullptr) {
-    if (s->host_registered) cudaHostUnregister(s->host);
+    if (s->host_registered) {
+      if (s->host_reg_piece == 0) {
+        cudaHostUnregister(s->host);
+      } else {
+        for (size_t off = 0; off < s->host_bytes; off += s->host_reg_piece)
+          cudaHostUnregister(static_cast<char*>(s->host) + off);
+      }
+    }
     if (s->host_is_shm) shmdt(s->host);
     else munmap(s->host, s->host_bytes);
     s->host = nullptr;
@@ -214,7 +222,34 @@ extern "C" int dgs_store_create(const int64_t* shape, int32_t ndim, int32_t esz,
     if (rc == DGS_OK) {
       cudaError_t e = cudaHostRegister(s->host, s->host_bytes, cudaHostRegisterDefault);
       if (e != cudaSuccess) {
+        // Seen on a 2-GPU run: pinning a 6.7 GB shared segment in one call failed with
+        // cudaErrorOperatingSystem while several ranks were pinning the same pages.  Registering the
+        // tail in 1 GiB pieces asks the OS for far less at a time; with UVA the pieces form one
+        // device-visible range at the host address.
+        cudaGetLastError();
+        int uva_same_ptr = 0, dev_id = 0;
+        cudaGetDevice(&dev_id);
+        cudaDeviceGetAttribute(&uva_same_ptr, cudaDevAttrCanUseHostPointerForRegisteredMem, dev_id);
+        const size_t piece = size_t(1) << 30;
+        size_t done = 0;
+        if (uva_same_ptr) {
+          e = cudaSuccess;
+          for (; done < s->host_bytes && e == cudaSuccess; done += piece) {
+            const size_t len = s->host_bytes - done < piece ? s->host_bytes - done : piece;
+            e = cudaHostRegister(static_cast<char*>(s->host) + done, len, cudaHostRegisterDefault);
+          }
+          if (e == cudaSuccess) {
+            s->host_reg_piece = piece;
+          } else {
+            for (size_t off = 0; off + piece < done; off += piece) cudaHostUnregister(static_cast<char*>(s->host) + off);
+          }
+        }
+      }
+      if (e != cudaSuccess) {
         rc = cuda_fail(e, "cudaHostRegister(host tail)", __FILE__, __LINE__);
+      } else if (s->host_reg_piece != 0) {
+        s->host_registered = true;
+        s->host_dev = s->host;
       } else {
         s->host_registered = true;
         e = cudaHostGetDevicePointer(&s->host_dev, s->host, 0);
