@@ -23,7 +23,8 @@ Printed JSON (rank 0, one line):
              the timed step is sample + relabel + gather
   e2e        same metric with the seeds coming from pinned host memory and a
              device->host read of the result inside the timed region
-  roofline   the gather kernel: algorithmic bytes / CUDA-event time vs measured HBM peak
+  roofline   the gather kernel: algorithmic bytes / CUDA-event time of back-to-back launches on the
+             last frontiers vs measured HBM peak (the in-step figure is given beside it)
   cpu_baseline  the CPU oracle (port of the reference algorithm) on a bounded sample
 
 `--impl reference` times that CPU port alone on all host threads (the reference

@@ -197,7 +197,8 @@ DGS_API int dgs_split_index_static(const dgs_chunk_desc* t, const void* idx, int
  * count(seed) = min(deg,k) without replacement, (deg ? k : 0) with.
  * `plan` is caller scratch of dgs_sample_plan_bytes(n) bytes that must stay
  * alive until the matching dgs_sample_* call has run.  If nnz != NULL the
- * total output size is written there by an extra small kernel. */
+ * total output size is written there by the plan kernel itself (its last CTA),
+ * i.e. before any sampling kernel enqueued behind it has run. */
 DGS_API size_t dgs_sample_plan_bytes(int64_t n_seeds);
 DGS_API int dgs_sample_plan(const dgs_chunk_desc* indptr, const void* seeds, int32_t ids64,
                     int64_t n_seeds, int64_t k, int32_t replace, void* plan,
