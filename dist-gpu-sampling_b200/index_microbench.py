@@ -31,7 +31,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, default=4_000_000)
     ap.add_argument("--dim", type=int, default=128)
-    ap.add_argument("--ids", type=int, default=1_000_000, help="row ids per query")
+    ap.add_argument("--ids", type=str, default="1000000",
+                    help="row ids per query; a comma-separated list runs one query size after the other")
     ap.add_argument("--host-frac", type=float, default=0.0, help="fraction of rows kept in the host tail")
     ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"])
     ap.add_argument("--id-window", type=int, default=0,
@@ -79,16 +80,28 @@ def main():
     if world > 1:
         dist.barrier()
 
+    id_counts = [int(x) for x in str(args.ids).split(",")]
+    hbm_cached = [args.hbm_peak]
+    for n_ids in id_counts:
+        run_query(args, n_ids, table, sub, host, each, world, rank, dev, synth, torch, hbm_cached)
+    del table, sub, host
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_query(args, n_ids, table, sub, host, each, world, rank, dev, synth, torch, hbm_cached):
+    D, rows = args.dim, args.rows
     g = torch.Generator(device=dev)
     g.manual_seed(100 + rank)
     if args.id_window > 0:
         per_gpu = each // D
-        ids = torch.randint(0, min(args.id_window, per_gpu), (args.ids,), device=dev, generator=g) \
+        ids = torch.randint(0, min(args.id_window, per_gpu), (n_ids,), device=dev, generator=g) \
             + ((rank + 1) % world) * per_gpu
     elif args.dist == "uniform":
-        ids = torch.randint(0, rows, (args.ids,), device=dev, generator=g)
+        ids = torch.randint(0, rows, (n_ids,), device=dev, generator=g)
     else:  # Zipf(1.1) ranks by inverse CDF, rank -> row through a fixed permutation
-        u = torch.rand(args.ids, device=dev, generator=g, dtype=torch.float64)
+        u = torch.rand(n_ids, device=dev, generator=g, dtype=torch.float64)
         a = 1.1
         r = ((1.0 - u * (1.0 - float(rows) ** (1.0 - a))) ** (1.0 / (1.0 - a))).floor().clamp_(1, rows).long() - 1
         gp = torch.Generator(device=dev)
@@ -108,12 +121,13 @@ def main():
         return out, ms[len(ms) // 2]
 
     # measured denominators
-    hbm = args.hbm_peak
+    hbm = hbm_cached[0]
     if hbm <= 0:
         a_ = torch.empty(1 << 28, dtype=torch.float32, device=dev)
         b_ = torch.empty_like(a_)
         _, ms = timed(lambda _: b_.copy_(a_), None)
         hbm = 2 * a_.numel() * 4 / ms / 1e6
+        hbm_cached[0] = hbm
         del a_, b_
     host_link = None
     if host.numel():
@@ -129,10 +143,11 @@ def main():
         k = min(2048, idx.numel())
         if k == 0:
             return True
-        sel = idx[:k]
-        flat = (sel[:, None] * D + torch.arange(D, device=dev)[None, :]).reshape(-1)
-        exp = synth.hash_of_index(flat).reshape(k, D)
-        return bool(torch.equal(out[:k], exp))
+        for sel, got in ((idx[:k], out[:k]), (idx[-k:], out[-k:])):      # both ends of the result
+            flat = (sel[:, None] * D + torch.arange(D, device=dev)[None, :]).reshape(-1)
+            if not torch.equal(got, synth.hash_of_index(flat).reshape(k, D)):
+                return False
+        return True
 
     cases = [("index (mixed)", table._CAPI_index, ids, None),
              ("local_index", table._CAPI_local_index, lo_ids, hbm),
@@ -144,7 +159,7 @@ def main():
             continue
         out, ms = timed(fn, idx)
         payload = idx.numel() * D * 4
-        line = {"case": name, "rank": rank, "world": world, "rows": idx.numel(), "dim": D, "dist": args.dist,
+        line = {"case": name, "rank": rank, "world": world, "ids": n_ids, "rows": idx.numel(), "dim": D, "dist": args.dist,
                 "ms": ms, "payload_gbs": payload / ms / 1e6,
                 "algorithmic_gbs": idx.numel() * (8 + 2 * D * 4) / ms / 1e6, "verified": verify(out, idx)}
         if name == "local_index":
@@ -157,10 +172,6 @@ def main():
                         split_index_ms=split_ms)
         if rank == 0 or name != "index (mixed)":
             print(json.dumps(line), flush=True)
-    del table, sub, host
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -111,6 +111,20 @@ def test_gather_large_is_index_select(words):
     assert torch.equal(gather(plain_desc(t100), idx[:500_000], 100, torch.float32, words), t100[idx[:500_000]])
 
 
+def test_gather_offsets_beyond_4_gib(words):
+    """Table and result both larger than 2^32 bytes: every byte offset is 64-bit."""
+    from gpu_util import plain_desc, gather
+    g = torch.Generator(device="cuda").manual_seed(2)
+    rows = 9_000_000                                     # x 512 B = 4.6 GB
+    table = torch.randint(-2 ** 31, 2 ** 31 - 1, (rows, 128), device="cuda", generator=g, dtype=torch.int32)
+    idx = torch.randint(0, rows, (rows,), device="cuda", generator=g)
+    idx[-1] = rows - 1
+    out = gather(plain_desc(table), idx, 128, torch.int32, words)
+    assert words.take_status() == 0
+    for lo in range(0, rows, 3_000_000):
+        assert torch.equal(out[lo:lo + 3_000_000], table[idx[lo:lo + 3_000_000]])
+
+
 def test_split_index_matches_oracle(oracle, words, pkg):
     from gpu_util import EmulatedChunks, vp
     abi = pkg.load_abi()
