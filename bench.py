@@ -71,6 +71,7 @@ def workload(args):
 LAUNCHES_SAMPLE = 2   # plan (+ tile scan in its last CTA), sample
 LAUNCHES_RELABEL = 4  # insert, count (+ tile scan in its last CTA), number, lookup
 LAUNCHES_GATHER = 1
+LAUNCHES_HOP_FUSED = 7  # plan, sample, clear, insert, count, number, lookup (+ 1 init kernel per step)
 # DRAM bytes per gathered row (read + write) from the ncu capture summarised in
 # profiles/; None until a capture exists for the benchmarked row width
 NCU_TRAFFIC_BYTES_PER_ROW = {100: 860.7}
@@ -90,6 +91,9 @@ def parse_args():
                     help="sample with per-edge fp32 U(0,1) weights (the weighted operator) instead of uniformly")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fused", action="store_true",
+                    help="run each step's hops through _CAPI_sample_blocks* (one queued sequence, one size "
+                         "read-back) instead of one sampling and one relabel operator per hop")
     return ap.parse_args()
 
 
@@ -327,7 +331,8 @@ def main_ours(args):
     torch.manual_seed(1234 + rank)
 
     def step(seeds):
-        frontier, blocks, n_edges = pkg.sample_blocks(seeds, fanouts, c_indptr, c_indices, probs=c_probs)
+        frontier, blocks, n_edges = pkg.sample_blocks(seeds, fanouts, c_indptr, c_indices, probs=c_probs,
+                                                      fused=args.fused)
         return frontier, n_edges
 
     def barrier():
@@ -437,7 +442,10 @@ def main_ours(args):
                           "gather_payload_gbs_all_ranks": rows_all * dim * 4 / (gather_ms * 1e-3) / 1e9},
             "e2e": {"value": e2e_edges_all / (e2e_ms * 1e-3), "unit": "edges/s",
                     "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * (len(fanouts) * (LAUNCHES_SAMPLE + LAUNCHES_RELABEL) + LAUNCHES_GATHER),
+            "gpu_launches": args.steps * ((1 + len(fanouts) * LAUNCHES_HOP_FUSED if args.fused else
+                                           len(fanouts) * (LAUNCHES_SAMPLE + LAUNCHES_RELABEL)) + LAUNCHES_GATHER),
+            "api": "_CAPI_sample_blocks* (all hops queued as one sequence)" if args.fused
+                   else "reference operator sequence: _CAPI_sample_neighbors* + _CAPI_tensor_relabel per hop",
             "roofline": {"kernel": "gather_rows_kernel (features._CAPI_index)", "bound": "hbm",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind,

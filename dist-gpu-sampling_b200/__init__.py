@@ -63,6 +63,7 @@ def load_ops():
 # ---------------------------------------------------------------------------
 DGS_MAX_PARTS = 8
 DGS_MAX_SEGMENTS = 8
+DGS_MAX_HOPS = 8
 
 
 class ChunkDesc(ctypes.Structure):
@@ -77,10 +78,16 @@ class Segments(ctypes.Structure):
                 ("ptr", ctypes.c_void_p * DGS_MAX_SEGMENTS), ("len", ctypes.c_int64 * DGS_MAX_SEGMENTS)]
 
 
+class Hop(ctypes.Structure):
+    _fields_ = [("fanout", ctypes.c_int64), ("seed_bound", ctypes.c_int64), ("frontier_bound", ctypes.c_int64),
+                ("coo_row", ctypes.c_void_p), ("coo_col", ctypes.c_void_p), ("frontier", ctypes.c_void_p)]
+
+
 # name -> (restype, argtypes); every symbol include/dgs_b200.h declares
 _I32, _I64, _U64, _VP, _SZ = ctypes.c_int32, ctypes.c_int64, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_size_t
 _DP, _SP = ctypes.POINTER(ChunkDesc), ctypes.POINTER(Segments)
 _I64P = ctypes.POINTER(ctypes.c_int64)
+_HP = ctypes.POINTER(Hop)
 ABI_SIGNATURES = {
     "dgs_last_error": (ctypes.c_char_p, []),
     "dgs_device_check": (ctypes.c_int, []),
@@ -114,6 +121,10 @@ ABI_SIGNATURES = {
     "dgs_relabel_table_bytes": (_SZ, [_I64]),
     "dgs_unique_first_occurrence": (ctypes.c_int, [_SP, _I32, _VP, _SZ, _VP, _VP, _VP, _VP]),
     "dgs_relabel_lookup": (ctypes.c_int, [_VP, _SZ, _I64, _SP, _I32, _VP, _VP]),
+    "dgs_sample_blocks_bounds": (ctypes.c_int, [_I64, _I64P, _I32, _I64, _HP]),
+    "dgs_sample_blocks_workspace_bytes": (_SZ, [_HP, _I32]),
+    "dgs_sample_blocks": (ctypes.c_int, [_DP, _DP, _DP, _VP, _I32, _HP, _I32, _I32, _U64, _U64, _VP, _SZ, _VP, _VP,
+                                         _VP]),
     "dgs_cache_table_slots": (_I64, [_I64]),
     "dgs_cache_build": (ctypes.c_int, [_VP, _VP, _I32, _I64, _VP, _VP, _I64, _VP, _VP]),
     "dgs_cache_fetch": (ctypes.c_int, [_VP, _I64, _DP, _VP, _I32, _I64, _I64, _VP, _VP, _I64, _VP, _VP, _VP]),
@@ -190,17 +201,32 @@ def create_chunktensor(tensor, num_gpus, available_mem, cache_rate=1.0, root_ran
     return ct
 
 
-def sample_blocks(seeds, fanouts, indptr, indices, probs=None, replace=False):
+def sample_blocks(seeds, fanouts, indptr, indices, probs=None, replace=False, fused=False):
     """The hot loop of ChunkTensorSampler.sample_blocks
     (chunktensor_sampler.py:93-118) without the DGL block objects.
 
     indptr / indices / probs are ChunkTensors or plain CUDA tensors.  Returns
     (frontier, blocks, n_edges) with blocks = [(coo_row, coo_col, n_src, n_dst)]
     in layer order (outermost hop first, like the reference's blocks.insert(0, ...)).
+
+    fused=False runs the reference's own sequence: one sampling operator and one
+    _CAPI_tensor_relabel per hop.  fused=True hands the whole loop to
+    _CAPI_sample_blocks*, which queues every hop without reading a size back in
+    between; the results follow the same rules (and are identical wherever no
+    random choice is involved).
     """
     import torch
     ops = torch.ops.dgs_ops
     chunked = not isinstance(indptr, torch.Tensor)
+    if fused:
+        if probs is not None:
+            fn = ops._CAPI_sample_blocks_with_probs_with_chunk_tensor if chunked else ops._CAPI_sample_blocks_with_probs
+            frontier, rows, cols, shape = fn(seeds, indptr, indices, probs, list(fanouts), replace)
+        else:
+            fn = ops._CAPI_sample_blocks_with_chunk_tensor if chunked else ops._CAPI_sample_blocks
+            frontier, rows, cols, shape = fn(seeds, indptr, indices, list(fanouts), replace)
+        blocks = [(rows[i], cols[i], shape[2 * i], shape[2 * i + 1]) for i in range(len(rows))]
+        return frontier, blocks, sum(r.numel() for r in rows)
     blocks, n_edges = [], 0
     for fan_out in reversed(list(fanouts)):
         if probs is not None:

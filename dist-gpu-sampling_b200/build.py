@@ -24,6 +24,7 @@ ABI_SOURCES = [
     "kernels/split.cu",
     "kernels/sample.cu",
     "kernels/relabel.cu",
+    "kernels/blocks.cu",
     "kernels/order.cu",
     "host/error.cc",
     "host/comm.cc",
@@ -33,6 +34,7 @@ HEADERS = [
     "kernels/common.cuh",
     "kernels/philox.cuh",
     "kernels/tile_scan.cuh",
+    "kernels/launchers.h",
     "host/comm.h",
     "../../include/dgs_b200.h",
 ]

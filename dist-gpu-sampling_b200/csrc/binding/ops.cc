@@ -40,8 +40,9 @@ namespace {
 
 // ---- pinned words the kernels write data-dependent sizes / status into ----
 struct HostWords {
-  int64_t* sizes = nullptr;  // [8]
-  int32_t* status = nullptr; // [1]
+  int64_t* sizes = nullptr;        // [8]
+  int32_t* status = nullptr;       // [1]
+  int64_t* block_sizes = nullptr;  // [2 * DGS_MAX_HOPS]
 };
 
 HostWords& host_words() {
@@ -49,11 +50,13 @@ HostWords& host_words() {
   static std::once_flag once;
   std::call_once(once, [] {
     void* p = nullptr;
-    TORCH_CHECK(cudaHostAlloc(&p, 128, cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess,
+    TORCH_CHECK(cudaHostAlloc(&p, 256, cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess,
                 "dgs: cannot allocate pinned status words");
-    std::memset(p, 0, 128);
+    std::memset(p, 0, 256);
     w.sizes = static_cast<int64_t*>(p);
     w.status = reinterpret_cast<int32_t*>(static_cast<char*>(p) + 64);
+    w.block_sizes = reinterpret_cast<int64_t*>(static_cast<char*>(p) + 128);
+    static_assert(2 * DGS_MAX_HOPS * sizeof(int64_t) <= 128, "block sizes do not fit");
   });
   return w;
 }
@@ -164,14 +167,15 @@ torch::Tensor make_locality_order(const dgs_chunk_desc& d, const torch::Tensor& 
 }
 
 // (seed, offset) from torch's default CUDA generator, so torch.manual_seed
-// controls sampling; each call consumes one offset step.
-std::pair<uint64_t, uint64_t> next_rng() {
+// controls sampling; a call that needs `streams` independent random streams uses
+// offset, offset + 1, ... and the generator moves past them.
+std::pair<uint64_t, uint64_t> next_rng(uint64_t streams = 1) {
   auto gen = at::get_generator_or_default<at::CUDAGeneratorImpl>(
       c10::nullopt, at::cuda::detail::getDefaultCUDAGenerator());
   std::lock_guard<std::mutex> lock(gen->mutex_);
   const uint64_t seed = gen->current_seed();
   const uint64_t offset = gen->get_offset();
-  gen->set_offset(offset + 4);
+  gen->set_offset(offset + 4 * ((streams + 3) / 4));  // torch keeps the offset a multiple of 4
   return {seed, offset};
 }
 
@@ -463,6 +467,149 @@ std::tuple<torch::Tensor, std::vector<torch::Tensor>> TensorRelabelCUDA(
 }
 
 // ===========================================================================
+// multi-hop sample + relabel in one queued sequence
+// ===========================================================================
+namespace {
+
+using BlocksResult =
+    std::tuple<torch::Tensor, std::vector<torch::Tensor>, std::vector<torch::Tensor>, std::vector<int64_t>>;
+
+// workspace + outputs the one-sequence path may hold (they are sized by upper
+// bounds, not by what the hops turn out to need); larger requests go hop by hop
+constexpr int64_t kBlocksBudgetBytes = int64_t(2) << 30;
+
+BlocksResult blocks_impl(torch::Tensor seeds, const dgs_chunk_desc& indptr, torch::ScalarType indptr_dtype,
+                         const dgs_chunk_desc& indices, torch::ScalarType indices_dtype,
+                         const dgs_chunk_desc* probs, const std::vector<int64_t>& fanouts, bool replace) {
+  CHECK_CUDA(seeds);
+  check_status("sample_blocks");
+  const bool ids64 = is_id64(seeds, "seeds");
+  TORCH_CHECK(seeds.scalar_type() == indptr_dtype && seeds.scalar_type() == indices_dtype,
+              "seeds, indptr and indices must share one id type");
+  const int H = static_cast<int>(fanouts.size());
+  TORCH_CHECK(H >= 1, "sample_blocks: no fan-outs");
+  for (int64_t k : fanouts) TORCH_CHECK(k >= 0, "num_picks must be >= 0");
+  c10::cuda::CUDAGuard guard(seeds.device());
+  seeds = seeds.contiguous().view({-1});
+  const int64_t n = seeds.numel();
+  const int64_t esz = ids64 ? 8 : 4;
+  // the reference applies the fan-outs last to first (chunktensor_sampler.py:97)
+  std::vector<int64_t> applied(fanouts.rbegin(), fanouts.rend());
+
+  std::vector<torch::Tensor> rows(H), cols(H);
+  std::vector<int64_t> shape(2 * H);
+  torch::Tensor frontier;
+
+  dgs_hop hops[DGS_MAX_HOPS];
+  bool sequence = n > 0 && H <= DGS_MAX_HOPS;
+  for (int64_t k : applied) sequence = sequence && k >= 1;
+  if (sequence) sequence = dgs_sample_blocks_bounds(n, applied.data(), H, indptr.total - 1, hops) == DGS_OK;
+  size_t ws_bytes = 0;
+  if (sequence) {
+    ws_bytes = dgs_sample_blocks_workspace_bytes(hops, H);
+    int64_t total = static_cast<int64_t>(ws_bytes);
+    for (int h = 0; h < H; ++h) total += (2 * hops[h].seed_bound * hops[h].fanout + hops[h].frontier_bound) * esz;
+    sequence = total <= kBlocksBudgetBytes;
+  }
+
+  if (!sequence) {
+    // hop by hop through the per-operator path (empty input, zero fan-outs, very large bounds)
+    torch::Tensor cur = seeds;
+    for (int h = 0; h < H; ++h) {
+      auto rc = sample_impl(cur, indptr, indptr_dtype, indices, indices_dtype, probs, applied[h], replace);
+      auto rl = TensorRelabelCUDA({cur, std::get<1>(rc)}, {std::get<0>(rc), std::get<1>(rc)});
+      const int at = H - 1 - h;
+      rows[at] = std::get<1>(rl)[0];
+      cols[at] = std::get<1>(rl)[1];
+      shape[2 * at] = std::get<0>(rl).numel();
+      shape[2 * at + 1] = cur.numel();
+      cur = std::get<0>(rl);
+    }
+    return std::make_tuple(cur, rows, cols, shape);
+  }
+
+  auto opt = seeds.options();
+  cudaStream_t stream = current_stream();
+  HostWords& w = host_words();
+  const auto rng = next_rng(static_cast<uint64_t>(H));
+  torch::Tensor ws = byte_scratch(ws_bytes, seeds.device());
+  std::vector<torch::Tensor> fr(H);
+  for (int h = 0; h < H; ++h) {
+    const int64_t cap = hops[h].seed_bound * hops[h].fanout;
+    rows[H - 1 - h] = torch::empty({cap}, opt);
+    cols[H - 1 - h] = torch::empty({cap}, opt);
+    fr[h] = torch::empty({hops[h].frontier_bound}, opt);
+    hops[h].coo_row = rows[H - 1 - h].data_ptr();
+    hops[h].coo_col = cols[H - 1 - h].data_ptr();
+    hops[h].frontier = fr[h].data_ptr();
+    w.block_sizes[2 * h] = w.block_sizes[2 * h + 1] = kPending;
+  }
+  DGS_CHECK_RC(dgs_sample_blocks(&indptr, &indices, probs, seeds.data_ptr(), ids64, hops, H, replace, rng.first,
+                                 rng.second, ws.data_ptr(), ws_bytes, w.block_sizes, w.status, stream));
+  // the one read-back: the last size lands while that hop's numbering and lookup still run
+  int64_t n_dst = n;
+  for (int h = 0; h < H; ++h) {
+    const int64_t nnz = wait_size(w.block_sizes + 2 * h, stream, "sample_blocks");
+    const int64_t nu = wait_size(w.block_sizes + 2 * h + 1, stream, "sample_blocks");
+    TORCH_CHECK(nnz >= 0 && nnz <= hops[h].seed_bound * hops[h].fanout && nu >= 0,
+                "dgs: sample_blocks returned an impossible size");
+    const int at = H - 1 - h;
+    rows[at] = rows[at].narrow(0, 0, nnz);
+    cols[at] = cols[at].narrow(0, 0, nnz);
+    shape[2 * at] = std::min(nu, hops[h].frontier_bound);
+    shape[2 * at + 1] = n_dst;
+    n_dst = shape[2 * at];
+  }
+  check_status("sample_blocks");
+  frontier = fr[H - 1].narrow(0, 0, n_dst);
+  return std::make_tuple(frontier, rows, cols, shape);
+}
+
+}  // namespace
+
+// (frontier, coo_rows, coo_cols, [n_src_0, n_dst_0, n_src_1, n_dst_1, ...]) with the blocks in layer
+// order, outermost hop first, as ChunkTensorSampler.sample_blocks builds its list
+BlocksResult SampleBlocksCUDA(torch::Tensor seeds, torch::Tensor indptr, torch::Tensor indices,
+                              std::vector<int64_t> fanouts, bool replace) {
+  CHECK_CUDA(indptr);
+  CHECK_CUDA(indices);
+  indptr = indptr.contiguous();
+  indices = indices.contiguous();
+  return blocks_impl(seeds, plain_desc(indptr), indptr.scalar_type(), plain_desc(indices), indices.scalar_type(),
+                     nullptr, fanouts, replace);
+}
+
+BlocksResult SampleBlocksWithChunkTensorCUDA(torch::Tensor seeds, c10::intrusive_ptr<ChunkTensor> indptr,
+                                             c10::intrusive_ptr<ChunkTensor> indices, std::vector<int64_t> fanouts,
+                                             bool replace) {
+  return blocks_impl(seeds, indptr->desc(), indptr->dtype(), indices->desc(), indices->dtype(), nullptr, fanouts,
+                     replace);
+}
+
+BlocksResult SampleBlocksProbCUDA(torch::Tensor seeds, torch::Tensor indptr, torch::Tensor indices,
+                                  torch::Tensor probs, std::vector<int64_t> fanouts, bool replace) {
+  CHECK_CUDA(indptr);
+  CHECK_CUDA(indices);
+  CHECK_CUDA(probs);
+  TORCH_CHECK(probs.scalar_type() == torch::kFloat, "probs must be float32");
+  indptr = indptr.contiguous();
+  indices = indices.contiguous();
+  probs = probs.contiguous();
+  const dgs_chunk_desc pd = plain_desc(probs);
+  return blocks_impl(seeds, plain_desc(indptr), indptr.scalar_type(), plain_desc(indices), indices.scalar_type(),
+                     &pd, fanouts, replace);
+}
+
+BlocksResult SampleBlocksProbWithChunkTensorCUDA(torch::Tensor seeds, c10::intrusive_ptr<ChunkTensor> indptr,
+                                                 c10::intrusive_ptr<ChunkTensor> indices,
+                                                 c10::intrusive_ptr<ChunkTensor> probs, std::vector<int64_t> fanouts,
+                                                 bool replace) {
+  TORCH_CHECK(probs->dtype() == torch::kFloat, "probs must be float32");
+  return blocks_impl(seeds, indptr->desc(), indptr->dtype(), indices->desc(), indices->dtype(), &probs->desc(),
+                     fanouts, replace);
+}
+
+// ===========================================================================
 // PaGraph-style cache
 // ===========================================================================
 std::tuple<torch::Tensor, torch::Tensor> CreateHashMapTensorCUDA(torch::Tensor input_key,
@@ -564,6 +711,10 @@ TORCH_LIBRARY(dgs_ops, m) {
       .def("_CAPI_sample_neighbors_with_chunk_tensor", &RowWiseSamplingUniformWithChunkTensorCUDA)
       .def("_CAPI_sample_neighbors_with_probs", &RowWiseSamplingProbCUDA)
       .def("_CAPI_sample_neighbors_with_probs_with_chunk_tensor", &RowWiseSamplingProbWithChunkTensorCUDA)
+      .def("_CAPI_sample_blocks", &SampleBlocksCUDA)
+      .def("_CAPI_sample_blocks_with_chunk_tensor", &SampleBlocksWithChunkTensorCUDA)
+      .def("_CAPI_sample_blocks_with_probs", &SampleBlocksProbCUDA)
+      .def("_CAPI_sample_blocks_with_probs_with_chunk_tensor", &SampleBlocksProbWithChunkTensorCUDA)
       .def("_CAPI_create_hash_map", &CreateHashMapTensorCUDA)
       .def("_CAPI_fetch_data", &FetchDataCUDA)
       .def("_CAPI_fetch_data_chunk_tensor", &FetchDataWithChunkTensorCUDA)

@@ -1,0 +1,190 @@
+// Multi-hop sample -> relabel as ONE queued launch sequence.
+//
+// Replaces the loop of ChunkTensorSampler.sample_blocks (reference
+// oppo_bench/single_node/utils/chunktensor_sampler.py:93-118), which for every
+// hop calls the sampling operator (one blocking size read-back,
+// src/cuda/rowwise_sampling.cu:147) and then the relabel operator (another one,
+// src/cuda/tensor_reindex.cu:129) from Python, so the GPU idles between hops
+// while the host learns each size and allocates the next output.
+//
+// Here the sizes never leave the device while the sequence runs: every kernel
+// takes its item count as a device word written by its predecessor (Count),
+// grids and buffers are sized by upper bounds the host can compute up front
+// (hop h has at most seeds_h * (1 + fanout_h) frontier nodes, and never more
+// than the graph has), and the actual sizes go to a caller-supplied (pinned)
+// array that the host reads once, after everything is queued.
+//
+// Per hop: plan -> sample -> clear table -> insert -> count -> number -> lookup.
+// From the second hop on the seed list is a relabel's unique list, so a seed's
+// relabelled id is its position and the sampler writes that directly; only the
+// first hop (whose seeds the caller may repeat) looks its rows up.
+#include "common.cuh"
+#include "launchers.h"
+
+namespace dgs {
+namespace {
+
+constexpr size_t WS_ALIGN = 256;
+inline size_t ws_align(size_t x) { return (x + WS_ALIGN - 1) / WS_ALIGN * WS_ALIGN; }
+
+struct InitWords {
+  int64_t* n0;
+  int64_t n0_value;
+  int n_tickets;
+  unsigned int* tickets[2 * DGS_MAX_HOPS];
+};
+
+__global__ void blocks_init_kernel(const InitWords w) {
+  if (threadIdx.x == 0) *w.n0 = w.n0_value;
+  if (threadIdx.x < w.n_tickets) *w.tickets[threadIdx.x] = 0u;
+}
+
+__global__ void zero_sizes_kernel(int64_t* sizes, int n) {
+  if (threadIdx.x < n) sizes[threadIdx.x] = 0;
+}
+
+int check_hops(const dgs_hop* hops, int32_t n_hops, const char* who) {
+  DGS_REQUIRE(hops != nullptr && n_hops >= 1 && n_hops <= DGS_MAX_HOPS, DGS_ERR_INVALID,
+              "%s: between 1 and %d hops", who, DGS_MAX_HOPS);
+  for (int h = 0; h < n_hops; ++h) {
+    DGS_REQUIRE(hops[h].fanout >= 1 && hops[h].seed_bound >= 0 && hops[h].frontier_bound >= 0, DGS_ERR_INVALID,
+                "%s: hop %d: fanout %lld, bounds %lld / %lld", who, h, (long long)hops[h].fanout,
+                (long long)hops[h].seed_bound, (long long)hops[h].frontier_bound);
+    DGS_REQUIRE(hops[h].seed_bound * (1 + hops[h].fanout) < (1ll << 30), DGS_ERR_UNSUPPORTED,
+                "%s: hop %d may produce %lld keys", who, h, (long long)(hops[h].seed_bound * (1 + hops[h].fanout)));
+    DGS_REQUIRE(h == 0 || hops[h].seed_bound == hops[h - 1].frontier_bound, DGS_ERR_INVALID,
+                "%s: hop %d: seed_bound must equal the previous hop's frontier_bound", who, h);
+  }
+  return DGS_OK;
+}
+
+}  // namespace
+}  // namespace dgs
+
+extern "C" int dgs_sample_blocks_bounds(int64_t n_seeds, const int64_t* fanouts, int32_t n_hops,
+                                        int64_t num_nodes, dgs_hop* hops) {
+  using namespace dgs;
+  DGS_REQUIRE(fanouts != nullptr && hops != nullptr && n_hops >= 1 && n_hops <= DGS_MAX_HOPS && n_seeds >= 0 &&
+                  num_nodes >= 0,
+              DGS_ERR_INVALID, "dgs_sample_blocks_bounds: bad arguments");
+  int64_t n = n_seeds;
+  for (int h = 0; h < n_hops; ++h) {
+    DGS_REQUIRE(fanouts[h] >= 1 && fanouts[h] < (1 << 20), DGS_ERR_INVALID, "dgs_sample_blocks_bounds: fanout %lld",
+                (long long)fanouts[h]);
+    hops[h].fanout = fanouts[h];
+    hops[h].seed_bound = n;
+    DGS_REQUIRE(n * (1 + fanouts[h]) < (1ll << 30), DGS_ERR_UNSUPPORTED,
+                "dgs_sample_blocks_bounds: hop %d may produce %lld keys", h, (long long)(n * (1 + fanouts[h])));
+    int64_t f = n * (1 + fanouts[h]);
+    // a frontier of valid ids cannot be longer than the node list
+    if (f > num_nodes) f = num_nodes > n ? num_nodes : n;
+    hops[h].frontier_bound = f;
+    n = f;
+  }
+  return DGS_OK;
+}
+
+extern "C" size_t dgs_sample_blocks_workspace_bytes(const dgs_hop* hops, int32_t n_hops) {
+  using namespace dgs;
+  if (hops == nullptr || n_hops < 1 || n_hops > DGS_MAX_HOPS) return 0;
+  size_t total = WS_ALIGN;  // control words
+  for (int h = 0; h < n_hops; ++h) {
+    total += ws_align(dgs_sample_plan_bytes(hops[h].seed_bound));
+    total += ws_align(dgs_relabel_table_bytes(hops[h].seed_bound * (1 + hops[h].fanout)));
+  }
+  return total;
+}
+
+extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_desc* indices,
+                                 const dgs_chunk_desc* probs, const void* seeds, int32_t ids64,
+                                 const dgs_hop* hops, int32_t n_hops, int32_t replace, uint64_t rng_seed,
+                                 uint64_t rng_offset, void* workspace, size_t workspace_bytes,
+                                 int64_t* sizes, int32_t* status, dgs_stream_t stream) {
+  using namespace dgs;
+  int rc = validate_desc(indptr, "dgs_sample_blocks(indptr)");
+  if (rc != DGS_OK) return rc;
+  rc = validate_desc(indices, "dgs_sample_blocks(indices)");
+  if (rc != DGS_OK) return rc;
+  if (probs != nullptr) {
+    rc = validate_desc(probs, "dgs_sample_blocks(probs)");
+    if (rc != DGS_OK) return rc;
+    DGS_REQUIRE(probs->esz == 4, DGS_ERR_UNSUPPORTED, "dgs_sample_blocks: weights must be fp32");
+  }
+  rc = check_hops(hops, n_hops, "dgs_sample_blocks");
+  if (rc != DGS_OK) return rc;
+  const int esz = ids64 ? 8 : 4;
+  DGS_REQUIRE(indptr->esz == esz && indices->esz == esz, DGS_ERR_INVALID,
+              "dgs_sample_blocks: indptr / indices element size does not match the id type");
+  DGS_REQUIRE(sizes != nullptr, DGS_ERR_INVALID, "dgs_sample_blocks: null sizes");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t n0 = hops[0].seed_bound;
+  if (n0 == 0) {
+    zero_sizes_kernel<<<1, 32, 0, s>>>(sizes, 2 * n_hops);
+    DGS_LAUNCH_CHECK();
+    return DGS_OK;
+  }
+  DGS_REQUIRE(seeds != nullptr, DGS_ERR_INVALID, "dgs_sample_blocks: null seeds");
+  DGS_REQUIRE(workspace != nullptr && workspace_bytes >= dgs_sample_blocks_workspace_bytes(hops, n_hops) &&
+                  (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+              DGS_ERR_INVALID, "dgs_sample_blocks: workspace too small or not 16-byte aligned");
+  for (int h = 0; h < n_hops; ++h) {
+    DGS_REQUIRE(hops[h].coo_row != nullptr && hops[h].coo_col != nullptr && hops[h].frontier != nullptr,
+                DGS_ERR_INVALID, "dgs_sample_blocks: hop %d: null output", h);
+    DGS_REQUIRE(probs == nullptr || replace || hops[h].fanout <= 32, DGS_ERR_UNSUPPORTED,
+                "dgs_sample_blocks: weighted fan-out %lld > 32 without replacement is not supported",
+                (long long)hops[h].fanout);
+  }
+
+  // ---- carve the workspace ----
+  char* p = static_cast<char*>(workspace);
+  int64_t* n0_dev = reinterpret_cast<int64_t*>(p);
+  p += WS_ALIGN;
+  void* plan[DGS_MAX_HOPS];
+  void* table[DGS_MAX_HOPS];
+  InitWords init{n0_dev, n0, 0, {}};
+  for (int h = 0; h < n_hops; ++h) {
+    const int64_t key_bound = hops[h].seed_bound * (1 + hops[h].fanout);
+    plan[h] = p;
+    p += ws_align(dgs_sample_plan_bytes(hops[h].seed_bound));
+    table[h] = p;
+    p += ws_align(dgs_relabel_table_bytes(key_bound));
+    init.tickets[init.n_tickets++] = sample_plan_ticket(plan[h], hops[h].seed_bound);
+    init.tickets[init.n_tickets++] = unique_ticket(table[h], key_bound);
+  }
+  blocks_init_kernel<<<1, 32, 0, s>>>(init);
+  DGS_LAUNCH_CHECK();
+
+  // ---- queue every hop; no size is read back in between ----
+  const void* hop_seeds = seeds;
+  const int64_t* n_dev = n0_dev;
+  for (int h = 0; h < n_hops; ++h) {
+    const dgs_hop& hp = hops[h];
+    const int64_t k = hp.fanout;
+    const int64_t edge_bound = hp.seed_bound * k;
+    const int64_t key_bound = hp.seed_bound + edge_bound;
+    const Count n{hp.seed_bound, n_dev, nullptr};
+    rc = launch_sample_plan(*indptr, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], &sizes[2 * h], false,
+                            status, s);
+    if (rc != DGS_OK) return rc;
+    const int64_t* nnz_dev = sample_plan_total(plan[h], hp.seed_bound);
+    const uint64_t key = sample_rng_key(rng_seed, rng_offset + static_cast<uint64_t>(h));
+    const bool row_is_position = h > 0;
+    rc = probs != nullptr
+             ? launch_sample_weighted(*indices, *probs, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], nullptr,
+                                      key, hp.coo_row, hp.coo_col, edge_bound, nullptr, row_is_position, status, s)
+             : launch_sample_uniform(*indices, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], nullptr, key,
+                                     hp.coo_row, hp.coo_col, edge_bound, nullptr, row_is_position, status, s);
+    if (rc != DGS_OK) return rc;
+    const Count nnz{edge_bound, nnz_dev, nullptr};
+    rc = launch_unique_pair(ids64 != 0, hop_seeds, n, hp.coo_col, nnz, key_bound, table[h], hp.frontier,
+                            hp.frontier_bound, &sizes[2 * h + 1], status, s);
+    if (rc != DGS_OK) return rc;
+    const Count n_keys{key_bound, n_dev, nnz_dev};
+    rc = launch_lookup_pair(table[h], key_bound, n_keys, ids64 != 0, row_is_position ? nullptr : hp.coo_row,
+                            hp.coo_col, nnz, hp.coo_row, hp.coo_col, s);
+    if (rc != DGS_OK) return rc;
+    hop_seeds = hp.frontier;
+    n_dev = unique_total(table[h], key_bound);
+  }
+  return DGS_OK;
+}

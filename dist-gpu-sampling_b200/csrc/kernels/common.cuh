@@ -44,9 +44,28 @@ static inline int esz_log2(int32_t esz) {
   }
 }
 
+// A number of items that the host knows exactly (dev == nullptr: it is `bound`)
+// or only as an upper bound, the exact value being the sum of one or two device
+// words written by an earlier kernel on the same stream.  Launch grids are sized
+// by `bound`; kernels work on count_of().  This is what lets a whole multi-hop
+// sample -> relabel sequence be queued without the host reading a size back.
+struct Count {
+  int64_t bound;
+  const int64_t* dev;
+  const int64_t* dev2;
+};
+static inline Count exact_count(int64_t n) { return Count{n, nullptr, nullptr}; }
+
 #ifdef __CUDACC__
 
 constexpr unsigned FULL_MASK = 0xffffffffu;
+
+__device__ __forceinline__ int64_t count_of(const Count& c) {
+  if (c.dev == nullptr) return c.bound;
+  int64_t v = *c.dev;
+  if (c.dev2 != nullptr) v += *c.dev2;
+  return v < c.bound ? (v < 0 ? 0 : v) : c.bound;
+}
 
 // Sticky status word: first error wins, later ones are dropped.
 __device__ __forceinline__ void raise_status(int32_t* status, int32_t code) {

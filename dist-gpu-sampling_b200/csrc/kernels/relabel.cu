@@ -23,6 +23,7 @@
 //     mistaken for an input index by a concurrent reader, so no third table.
 //   * the number of distinct keys goes to a caller-supplied (pinned) word.
 #include "common.cuh"
+#include "launchers.h"
 #include "philox.cuh"
 #include "tile_scan.cuh"
 
@@ -51,17 +52,24 @@ struct TableView {
   int64_t ntiles;
 };
 
-inline uint64_t table_capacity(int64_t n) {
+// slots in use for a table built from n keys: the power of two >= max(2n, 64)
+__host__ __device__ __forceinline__ uint64_t slots_for(int64_t n) {
+  uint64_t want = 2 * static_cast<uint64_t>(n);
+  if (want < 64) want = 64;
+#ifdef __CUDA_ARCH__
+  return 1ull << (64 - __clzll(static_cast<long long>(want - 1)));
+#else
   uint64_t cap = 64;
-  while (cap < 2 * static_cast<uint64_t>(n)) cap <<= 1;
+  while (cap < want) cap <<= 1;
   return cap;
+#endif
 }
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 inline TableView table_view(void* mem, int64_t n) {
   TableView t;
-  t.cap = table_capacity(n);
+  t.cap = slots_for(n);
   t.ntiles = (n + RL_TILE - 1) / RL_TILE;
   char* p = static_cast<char*>(mem);
   t.slots = reinterpret_cast<Slot*>(p);
@@ -81,15 +89,55 @@ __device__ __forceinline__ uint64_t hash_key(long long key) {
   return z ^ (z >> 33);
 }
 
-// pass 1: insert every key, keep the smallest input index per key
-template <typename IdT>
+// ---- where the keys come from ---------------------------------------------------
+// A host-known segment list (the per-operator entry points) ...
+struct SegKeys {
+  dgs_segments s;
+  int64_t n;
+  __device__ __forceinline__ int64_t size() const { return n; }
+  template <typename IdT>
+  __device__ __forceinline__ IdT load(int64_t i) const {
+    return seg_load<IdT>(s, i);
+  }
+};
+// ... or two arrays a[0:na) ++ b[0:nb) whose lengths are device words (the
+// multi-hop sequence: a = this hop's seeds, b = the neighbours just sampled).
+struct PairKeys {
+  const void* a;
+  const void* b;
+  Count na, nb;
+  __device__ __forceinline__ int64_t size() const { return count_of(na) + count_of(nb); }
+  template <typename IdT>
+  __device__ __forceinline__ IdT load(int64_t i) const {
+    const int64_t x = count_of(na);
+    return i < x ? static_cast<const IdT*>(a)[i] : static_cast<const IdT*>(b)[i - x];
+  }
+};
+
+// pass 0 of the sequence with device-side counts: clear only the slots the actual
+// key count will use (the per-operator path clears with a memset instead)
 __global__ void __launch_bounds__(RL_BLOCK)
-relabel_insert_kernel(const __grid_constant__ dgs_segments keys, const int64_t n, Slot* slots,
-                      const uint64_t mask, uint32_t* __restrict__ slot_of,
+relabel_clear_kernel(Slot* __restrict__ slots, const Count n_keys) {
+  const uint64_t cap = slots_for(count_of(n_keys));
+  const uint64_t i = static_cast<uint64_t>(blockIdx.x) * (RL_BLOCK * 4) + threadIdx.x;
+  const ulonglong2 empty = make_ulonglong2(~0ull, ~0ull);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const uint64_t at = i + static_cast<uint64_t>(u) * RL_BLOCK;
+    if (at < cap) *reinterpret_cast<ulonglong2*>(&slots[at]) = empty;
+  }
+}
+
+// pass 1: insert every key, keep the smallest input index per key
+template <typename IdT, typename Keys>
+__global__ void __launch_bounds__(RL_BLOCK)
+relabel_insert_kernel(const __grid_constant__ Keys keys, Slot* slots, uint32_t* __restrict__ slot_of,
                       int32_t* __restrict__ status) {
+  const int64_t n = keys.size();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
   if (i >= n) return;
-  const long long key = static_cast<long long>(seg_load<IdT>(keys, i));
+  const uint64_t mask = slots_for(n) - 1;
+  const long long key = static_cast<long long>(keys.template load<IdT>(i));
   if (key < 0) {
     raise_status(status, DGS_ERR_RANGE);
     slot_of[i] = NO_SLOT;
@@ -123,13 +171,14 @@ relabel_insert_kernel(const __grid_constant__ dgs_segments keys, const int64_t n
 // the last CTA to finish turns the per-tile counts into offsets and publishes
 // the number of distinct keys
 __global__ void __launch_bounds__(RL_BLOCK)
-relabel_count_kernel(const int64_t n, const Slot* __restrict__ slots,
+relabel_count_kernel(const Count nc, const Slot* __restrict__ slots,
                      const uint32_t* __restrict__ slot_of, int64_t* tile_sums, unsigned int* ticket,
                      int64_t* total_dev, int64_t* n_unique_out) {
   __shared__ int s_cnt;
   __shared__ int64_t s_scan[RL_BLOCK / 32 + 1];
   if (threadIdx.x == 0) s_cnt = 0;
   __syncthreads();
+  const int64_t n = count_of(nc);
   const int64_t base = static_cast<int64_t>(blockIdx.x) * RL_TILE + threadIdx.x * RL_ITEMS;
   int c = 0;
 #pragma unroll
@@ -149,12 +198,13 @@ relabel_count_kernel(const int64_t n, const Slot* __restrict__ slots,
 }
 
 // pass 3: number the first occurrences, emit them, store the label in the slot
-template <typename IdT>
+template <typename IdT, typename Keys>
 __global__ void __launch_bounds__(RL_BLOCK)
-relabel_number_kernel(const __grid_constant__ dgs_segments keys, const int64_t n, Slot* slots,
-                      const uint32_t* __restrict__ slot_of, const int64_t* __restrict__ tile_off,
-                      IdT* __restrict__ unique_out) {
+relabel_number_kernel(const __grid_constant__ Keys keys, Slot* slots, const uint32_t* __restrict__ slot_of,
+                      const int64_t* __restrict__ tile_off, IdT* __restrict__ unique_out,
+                      const int64_t unique_capacity, int32_t* __restrict__ status) {
   __shared__ int smem[RL_BLOCK / 32 + 1];
+  const int64_t n = keys.size();
   const int64_t base = static_cast<int64_t>(blockIdx.x) * RL_TILE + threadIdx.x * RL_ITEMS;
   bool first[RL_ITEMS];
   uint32_t slot[RL_ITEMS];
@@ -179,11 +229,24 @@ relabel_number_kernel(const __grid_constant__ dgs_segments keys, const int64_t n
 #pragma unroll
   for (int u = 0; u < RL_ITEMS; ++u) {
     if (first[u]) {
-      unique_out[label] = seg_load<IdT>(keys, base + u);
+      if (label < unique_capacity) unique_out[label] = keys.template load<IdT>(base + u);
+      else raise_status(status, DGS_ERR_RANGE);
       slots[slot[u]].val = LABEL_BIT | static_cast<unsigned long long>(label);
       ++label;
     }
   }
+}
+
+__device__ __forceinline__ long long probe_label(const Slot* __restrict__ slots, uint64_t mask, long long key) {
+  if (key < 0) return -1;
+  uint64_t h = hash_key(key) & mask;
+  for (uint64_t probes = 0; probes <= mask; ++probes) {
+    const Slot s = slots[h];  // one 16-byte load
+    if (s.key == key) return static_cast<long long>(s.val & ~LABEL_BIT);
+    if (s.key == EMPTY_KEY) break;
+    h = (h + 1) & mask;
+  }
+  return -1;
 }
 
 // lookup: label of each id, -1 when absent
@@ -193,21 +256,22 @@ relabel_lookup_kernel(const __grid_constant__ dgs_segments in, const int64_t n,
                       const Slot* __restrict__ slots, const uint64_t mask, IdT* __restrict__ out) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
   if (i >= n) return;
-  const long long key = static_cast<long long>(seg_load<IdT>(in, i));
-  IdT res = static_cast<IdT>(-1);
-  if (key >= 0) {
-    uint64_t h = hash_key(key) & mask;
-    for (uint64_t probes = 0; probes <= mask; ++probes) {
-      const Slot s = slots[h];  // one 16-byte load
-      if (s.key == key) {
-        res = static_cast<IdT>(s.val & ~LABEL_BIT);
-        break;
-      }
-      if (s.key == EMPTY_KEY) break;
-      h = (h + 1) & mask;
-    }
-  }
-  out[i] = res;
+  out[i] = static_cast<IdT>(probe_label(slots, mask, static_cast<long long>(seg_load<IdT>(in, i))));
+}
+
+// lookup of the sequence with device-side counts: two id arrays of the same
+// (device) length, relabelled into two outputs (in place is fine); a == nullptr
+// skips the first array
+template <typename IdT>
+__global__ void __launch_bounds__(RL_BLOCK)
+relabel_lookup_pair_kernel(const IdT* a, const IdT* b, const Count nc, const Count n_keys,
+                           const Slot* __restrict__ slots, IdT* out_a, IdT* out_b) {
+  const int64_t n = count_of(nc);
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
+  if (i >= n) return;
+  const uint64_t mask = slots_for(count_of(n_keys)) - 1;
+  if (a != nullptr) out_a[i] = static_cast<IdT>(probe_label(slots, mask, static_cast<long long>(a[i])));
+  out_b[i] = static_cast<IdT>(probe_label(slots, mask, static_cast<long long>(b[i])));
 }
 
 inline int64_t seg_total(const dgs_segments& s) {
@@ -227,31 +291,69 @@ int check_segments(const dgs_segments* s, const char* who) {
 
 __global__ void zero_word_kernel(int64_t* w) { *w = 0; }
 
-template <typename IdT>
-int run_unique(const dgs_segments& keys, int64_t n, const TableView& t, void* unique_out,
+// insert -> count -> number over a cleared table; n_bound sizes the grids
+template <typename IdT, typename Keys>
+int run_unique(const Keys& keys, Count n_keys, const TableView& t, void* unique_out, int64_t unique_capacity,
                int64_t* n_unique, int32_t* status, cudaStream_t s) {
-  DGS_CUDA_TRY(cudaMemsetAsync(t.slots, 0xFF, t.cap * sizeof(Slot), s));
-  DGS_CUDA_TRY(cudaMemsetAsync(t.ticket, 0, sizeof(unsigned int), s));
-  const unsigned per_key_grid = static_cast<unsigned>((n + RL_BLOCK - 1) / RL_BLOCK);
-  relabel_insert_kernel<IdT><<<per_key_grid, RL_BLOCK, 0, s>>>(keys, n, t.slots, t.cap - 1, t.slot_of, status);
+  const unsigned per_key_grid = static_cast<unsigned>((n_keys.bound + RL_BLOCK - 1) / RL_BLOCK);
+  relabel_insert_kernel<IdT, Keys><<<per_key_grid, RL_BLOCK, 0, s>>>(keys, t.slots, t.slot_of, status);
   DGS_LAUNCH_CHECK();
-  relabel_count_kernel<<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(n, t.slots, t.slot_of, t.tile_off,
+  relabel_count_kernel<<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(n_keys, t.slots, t.slot_of, t.tile_off,
                                                                             t.ticket, t.total, n_unique);
   DGS_LAUNCH_CHECK();
-  relabel_number_kernel<IdT><<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(
-      keys, n, t.slots, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out));
+  relabel_number_kernel<IdT, Keys><<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(
+      keys, t.slots, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out), unique_capacity, status);
   DGS_LAUNCH_CHECK();
   return DGS_OK;
 }
 
 }  // namespace
+
+int64_t* unique_total(void* table, int64_t key_bound) { return table_view(table, key_bound).total; }
+unsigned int* unique_ticket(void* table, int64_t key_bound) { return table_view(table, key_bound).ticket; }
+
+int launch_unique_pair(bool ids64, const void* a, Count na, const void* b, Count nb, int64_t key_bound,
+                       void* table, void* unique_out, int64_t unique_capacity, int64_t* n_unique_out,
+                       int32_t* status, cudaStream_t s) {
+  DGS_REQUIRE(key_bound > 0 && key_bound < (1ll << 30) && na.bound + nb.bound <= key_bound, DGS_ERR_UNSUPPORTED,
+              "relabel: %lld keys", (long long)key_bound);
+  const TableView t = table_view(table, key_bound);
+  const Count n_keys{key_bound, na.dev, nb.dev};
+  DGS_REQUIRE(na.dev != nullptr && nb.dev != nullptr && na.dev2 == nullptr && nb.dev2 == nullptr, DGS_ERR_INVALID,
+              "relabel: the pair form takes one device word per length");
+  const PairKeys keys{a, b, na, nb};
+  const uint64_t cap = slots_for(key_bound);
+  relabel_clear_kernel<<<static_cast<unsigned>((cap + RL_BLOCK * 4 - 1) / (RL_BLOCK * 4)), RL_BLOCK, 0, s>>>(t.slots,
+                                                                                                          n_keys);
+  DGS_LAUNCH_CHECK();
+  return ids64 ? run_unique<int64_t, PairKeys>(keys, n_keys, t, unique_out, unique_capacity, n_unique_out, status, s)
+               : run_unique<int32_t, PairKeys>(keys, n_keys, t, unique_out, unique_capacity, n_unique_out, status, s);
+}
+
+int launch_lookup_pair(const void* table, int64_t key_bound, Count n_keys, bool ids64, const void* a,
+                       const void* b, Count n, void* out_a, void* out_b, cudaStream_t s) {
+  if (n.bound == 0) return DGS_OK;
+  const TableView t = table_view(const_cast<void*>(table), key_bound);
+  const unsigned grid = static_cast<unsigned>((n.bound + RL_BLOCK - 1) / RL_BLOCK);
+  if (ids64)
+    relabel_lookup_pair_kernel<int64_t><<<grid, RL_BLOCK, 0, s>>>(
+        static_cast<const int64_t*>(a), static_cast<const int64_t*>(b), n, n_keys, t.slots,
+        static_cast<int64_t*>(out_a), static_cast<int64_t*>(out_b));
+  else
+    relabel_lookup_pair_kernel<int32_t><<<grid, RL_BLOCK, 0, s>>>(
+        static_cast<const int32_t*>(a), static_cast<const int32_t*>(b), n, n_keys, t.slots,
+        static_cast<int32_t*>(out_a), static_cast<int32_t*>(out_b));
+  DGS_LAUNCH_CHECK();
+  return DGS_OK;
+}
+
 }  // namespace dgs
 
 extern "C" size_t dgs_relabel_table_bytes(int64_t n) {
   using namespace dgs;
   if (n < 0) n = 0;
   const int64_t ntiles = (n + RL_TILE - 1) / RL_TILE;
-  return table_capacity(n) * sizeof(Slot) + align_up(static_cast<size_t>(n) * sizeof(uint32_t), 16) +
+  return slots_for(n) * sizeof(Slot) + align_up(static_cast<size_t>(n) * sizeof(uint32_t), 16) +
          static_cast<size_t>(ntiles + 2) * sizeof(int64_t);
 }
 
@@ -279,8 +381,11 @@ extern "C" int dgs_unique_first_occurrence(const dgs_segments* keys, int32_t ids
     return DGS_OK;
   }
   DGS_REQUIRE(unique_out != nullptr, DGS_ERR_INVALID, "dgs_unique_first_occurrence: null output");
-  return ids64 ? run_unique<int64_t>(*keys, n, t, unique_out, n_unique, status, s)
-               : run_unique<int32_t>(*keys, n, t, unique_out, n_unique, status, s);
+  DGS_CUDA_TRY(cudaMemsetAsync(t.slots, 0xFF, t.cap * sizeof(Slot), s));
+  DGS_CUDA_TRY(cudaMemsetAsync(t.ticket, 0, sizeof(unsigned int), s));
+  const SegKeys sk{*keys, n};
+  return ids64 ? run_unique<int64_t, SegKeys>(sk, exact_count(n), t, unique_out, n, n_unique, status, s)
+               : run_unique<int32_t, SegKeys>(sk, exact_count(n), t, unique_out, n, n_unique, status, s);
 }
 
 extern "C" int dgs_relabel_lookup(const void* table, size_t table_bytes, int64_t n_keys_built,

@@ -44,6 +44,7 @@
 //     over seeds, so even a 1 024-seed hop fills the machine with independent
 //     short chains instead of a few long ones.
 #include "common.cuh"
+#include "launchers.h"
 #include "philox.cuh"
 #include "tile_scan.cuh"
 
@@ -91,12 +92,13 @@ __device__ __forceinline__ int64_t pick_count(int64_t deg, int64_t k, bool repla
 template <typename IdT>
 __global__ void __launch_bounds__(SAMPLE_BLOCK)
 sample_plan_kernel(const __grid_constant__ dgs_chunk_desc indptr, const IdT* __restrict__ seeds,
-                   const int64_t n, const int64_t k, const bool replace,
+                   const Count nc, const int64_t k, const bool replace,
                    int64_t* __restrict__ row_begin, int64_t* __restrict__ deg_out,
                    int64_t* __restrict__ local_off, int64_t* tile_sums, int64_t* total_out,
                    unsigned int* ticket, int64_t* nnz_out, int32_t* __restrict__ status) {
   __shared__ int64_t smem[SAMPLE_BLOCK / 32 + 1];
   constexpr int sh = sizeof(IdT) == 8 ? 3 : 2;
+  const int64_t n = count_of(nc);
   const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + threadIdx.x;
   int64_t cnt = 0;
   if (i < n) {
@@ -182,13 +184,14 @@ __device__ __forceinline__ SeedPlan seed_plan(const int64_t* __restrict__ plan_r
 template <typename IdT, int G>
 __global__ void __launch_bounds__(SAMPLE_BLOCK)
 sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT* __restrict__ seeds,
-                      const int64_t n, const int64_t k, const bool replace,
+                      const Count nc, const int64_t k, const bool replace,
                       const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
                       const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
                       const uint32_t* __restrict__ order, const uint64_t key, IdT* coo_row, IdT* coo_col,
                       const int64_t out_capacity, int64_t* __restrict__ picked_pos,
-                      int32_t* __restrict__ status) {
+                      const bool row_is_position, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
+  const int64_t n = count_of(nc);
   constexpr int GROUPS = SAMPLE_BLOCK / G;  // seeds per CTA
   const int lane = threadIdx.x & 31;
   const int l = threadIdx.x % G;        // lane inside the group
@@ -204,7 +207,7 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
     const int64_t i = (valid && order != nullptr) ? static_cast<int64_t>(order[slot]) : slot;
     const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, valid);
     const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
-    const int64_t seed = valid ? static_cast<int64_t>(seeds[i]) : 0;
+    const int64_t seed = !valid ? 0 : (row_is_position ? i : static_cast<int64_t>(seeds[i]));
     const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
 
     if (replace) {
@@ -397,13 +400,14 @@ template <typename IdT>
 __global__ void __launch_bounds__(SAMPLE_BLOCK)
 sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
                        const __grid_constant__ dgs_chunk_desc probs, const IdT* __restrict__ seeds,
-                       const int64_t n, const int64_t k, const bool replace,
+                       const Count nc, const int64_t k, const bool replace,
                        const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
                        const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
                        const uint32_t* __restrict__ order, const uint64_t key, IdT* coo_row, IdT* coo_col,
                        const int64_t out_capacity, int64_t* __restrict__ picked_pos,
-                       int32_t* __restrict__ status) {
+                       const bool row_is_position, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
+  const int64_t n = count_of(nc);
   const int l = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   constexpr int WARPS = SAMPLE_BLOCK / 32;
@@ -422,7 +426,7 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
     const int64_t i = order != nullptr ? static_cast<int64_t>(order[slot]) : slot;
     const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, true);
     const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
-    const int64_t seed = static_cast<int64_t>(seeds[i]);
+    const int64_t seed = row_is_position ? i : static_cast<int64_t>(seeds[i]);
     const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
     if (deg <= 0) break;
 
@@ -522,16 +526,25 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
           if (!(nk > top.thresh)) break;
           top.insert(nk, s_mpos[ww][t], l, static_cast<int>(k));
         }
-      if (l < k) emit(o, l, static_cast<int64_t>(seeds[i]), rb, top.pos);
+      if (l < k) emit(o, l, row_is_position ? i : static_cast<int64_t>(seeds[i]), rb, top.pos);
     }
     __syncthreads();
   }
 }
 
+__global__ void copy_total_kernel(const int64_t* total, int64_t* nnz) { *nnz = *total; }
+__global__ void zero_total_kernel(int64_t* nnz) { *nnz = 0; }
+
+int check_sample_args(const char* who, const void* seeds, int64_t n, int64_t k, const void* plan) {
+  DGS_REQUIRE(n >= 0 && k >= 0, DGS_ERR_INVALID, "%s: n=%lld k=%lld", who, (long long)n, (long long)k);
+  DGS_REQUIRE(n == 0 || (seeds != nullptr && plan != nullptr), DGS_ERR_INVALID, "%s: null buffer", who);
+  DGS_REQUIRE(n / (SAMPLE_BLOCK / 32) < 0x7fffffffLL, DGS_ERR_UNSUPPORTED, "%s: too many seeds", who);
+  return DGS_OK;
+}
+
 template <typename IdT>
-int launch_plan(const dgs_chunk_desc& indptr, const void* seeds, int64_t n, int64_t k, bool replace,
-                const PlanView& pv, int64_t* nnz, int32_t* status, cudaStream_t s) {
-  DGS_CUDA_TRY(cudaMemsetAsync(pv.ticket, 0, sizeof(unsigned int), s));
+int plan_typed(const dgs_chunk_desc& indptr, const void* seeds, Count n, int64_t k, bool replace,
+               const PlanView& pv, int64_t* nnz, int32_t* status, cudaStream_t s) {
   sample_plan_kernel<IdT><<<static_cast<unsigned>(pv.ntiles), SAMPLE_BLOCK, 0, s>>>(
       indptr, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
       pv.tile_off, pv.total, pv.ticket, nnz, status);
@@ -539,19 +552,16 @@ int launch_plan(const dgs_chunk_desc& indptr, const void* seeds, int64_t n, int6
   return DGS_OK;
 }
 
-__global__ void copy_total_kernel(const int64_t* total, int64_t* nnz) { *nnz = *total; }
-__global__ void zero_total_kernel(int64_t* nnz) { *nnz = 0; }
-
 template <typename IdT>
-int launch_uniform(const dgs_chunk_desc& indices, const void* seeds, int64_t n, int64_t k,
-                   bool replace, const PlanView& pv, const uint32_t* order, uint64_t key, void* coo_row,
-                   void* coo_col,
-                   int64_t cap, int64_t* pos, int32_t* status, cudaStream_t s) {
-#define DGS_LAUNCH_U(G)                                                                            \
-  sample_uniform_kernel<IdT, G>                                                                    \
-      <<<static_cast<unsigned>((n + SAMPLE_BLOCK / G - 1) / (SAMPLE_BLOCK / G)), SAMPLE_BLOCK, 0, s>>>( \
-          indices, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off, \
-          pv.tile_off, order, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, status)
+int uniform_typed(const dgs_chunk_desc& indices, const void* seeds, Count n, int64_t k, bool replace,
+                  const PlanView& pv, const uint32_t* order, uint64_t key, void* coo_row, void* coo_col,
+                  int64_t cap, int64_t* pos, bool rowpos, int32_t* status, cudaStream_t s) {
+#define DGS_LAUNCH_U(G)                                                                                  \
+  sample_uniform_kernel<IdT, G>                                                                          \
+      <<<static_cast<unsigned>((n.bound + SAMPLE_BLOCK / G - 1) / (SAMPLE_BLOCK / G)), SAMPLE_BLOCK, 0, s>>>( \
+          indices, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,    \
+          pv.tile_off, order, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, rowpos, \
+          status)
   if (k <= 4) DGS_LAUNCH_U(4);
   else if (k <= 8) DGS_LAUNCH_U(8);
   else if (k <= 16) DGS_LAUNCH_U(16);
@@ -561,14 +571,59 @@ int launch_uniform(const dgs_chunk_desc& indices, const void* seeds, int64_t n, 
   return DGS_OK;
 }
 
-int check_sample_args(const char* who, const void* seeds, int64_t n, int64_t k, const void* plan) {
-  DGS_REQUIRE(n >= 0 && k >= 0, DGS_ERR_INVALID, "%s: n=%lld k=%lld", who, (long long)n, (long long)k);
-  DGS_REQUIRE(n == 0 || (seeds != nullptr && plan != nullptr), DGS_ERR_INVALID, "%s: null buffer", who);
-  DGS_REQUIRE(n / (SAMPLE_BLOCK / 32) < 0x7fffffffLL, DGS_ERR_UNSUPPORTED, "%s: too many seeds", who);
+template <typename IdT>
+int weighted_typed(const dgs_chunk_desc& indices, const dgs_chunk_desc& probs, const void* seeds, Count n,
+                   int64_t k, bool replace, const PlanView& pv, const uint32_t* order, uint64_t key,
+                   void* coo_row, void* coo_col, int64_t cap, int64_t* pos, bool rowpos, int32_t* status,
+                   cudaStream_t s) {
+  const unsigned grid = static_cast<unsigned>((n.bound + SAMPLE_BLOCK / 32 - 1) / (SAMPLE_BLOCK / 32));
+  sample_weighted_kernel<IdT><<<grid, SAMPLE_BLOCK, 0, s>>>(
+      indices, probs, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
+      pv.tile_off, order, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, rowpos, status);
+  DGS_LAUNCH_CHECK();
   return DGS_OK;
 }
 
 }  // namespace
+
+int64_t* sample_plan_total(void* plan, int64_t n_bound) { return plan_view(plan, n_bound).total; }
+unsigned int* sample_plan_ticket(void* plan, int64_t n_bound) { return plan_view(plan, n_bound).ticket; }
+
+uint64_t sample_rng_key(uint64_t rng_seed, uint64_t rng_offset) {
+  return mix64(rng_seed) ^ mix64(rng_offset ^ 0xA5A5A5A55A5A5A5Aull);
+}
+
+int launch_sample_plan(const dgs_chunk_desc& indptr, const void* seeds, bool ids64, Count n, int64_t k,
+                       bool replace, void* plan, int64_t* nnz_out, bool zero_ticket, int32_t* status,
+                       cudaStream_t s) {
+  const PlanView pv = plan_view(plan, n.bound);
+  if (zero_ticket) DGS_CUDA_TRY(cudaMemsetAsync(pv.ticket, 0, sizeof(unsigned int), s));
+  return ids64 ? plan_typed<int64_t>(indptr, seeds, n, k, replace, pv, nnz_out, status, s)
+               : plan_typed<int32_t>(indptr, seeds, n, k, replace, pv, nnz_out, status, s);
+}
+
+int launch_sample_uniform(const dgs_chunk_desc& indices, const void* seeds, bool ids64, Count n, int64_t k,
+                          bool replace, void* plan, const uint32_t* order, uint64_t key, void* coo_row,
+                          void* coo_col, int64_t out_capacity, int64_t* picked_pos, bool row_is_position,
+                          int32_t* status, cudaStream_t s) {
+  const PlanView pv = plan_view(plan, n.bound);
+  return ids64 ? uniform_typed<int64_t>(indices, seeds, n, k, replace, pv, order, key, coo_row, coo_col,
+                                        out_capacity, picked_pos, row_is_position, status, s)
+               : uniform_typed<int32_t>(indices, seeds, n, k, replace, pv, order, key, coo_row, coo_col,
+                                        out_capacity, picked_pos, row_is_position, status, s);
+}
+
+int launch_sample_weighted(const dgs_chunk_desc& indices, const dgs_chunk_desc& probs, const void* seeds,
+                           bool ids64, Count n, int64_t k, bool replace, void* plan, const uint32_t* order,
+                           uint64_t key, void* coo_row, void* coo_col, int64_t out_capacity,
+                           int64_t* picked_pos, bool row_is_position, int32_t* status, cudaStream_t s) {
+  const PlanView pv = plan_view(plan, n.bound);
+  return ids64 ? weighted_typed<int64_t>(indices, probs, seeds, n, k, replace, pv, order, key, coo_row, coo_col,
+                                         out_capacity, picked_pos, row_is_position, status, s)
+               : weighted_typed<int32_t>(indices, probs, seeds, n, k, replace, pv, order, key, coo_row, coo_col,
+                                         out_capacity, picked_pos, row_is_position, status, s);
+}
+
 }  // namespace dgs
 
 extern "C" size_t dgs_sample_plan_bytes(int64_t n) {
@@ -595,9 +650,7 @@ extern "C" int dgs_sample_plan(const dgs_chunk_desc* indptr, const void* seeds, 
     }
     return DGS_OK;
   }
-  const PlanView pv = plan_view(plan, n);
-  return ids64 ? launch_plan<int64_t>(*indptr, seeds, n, k, replace != 0, pv, nnz, status, s)
-               : launch_plan<int32_t>(*indptr, seeds, n, k, replace != 0, pv, nnz, status, s);
+  return launch_sample_plan(*indptr, seeds, ids64 != 0, exact_count(n), k, replace != 0, plan, nnz, true, status, s);
 }
 
 extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* seeds, int32_t ids64,
@@ -622,15 +675,12 @@ extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* see
   }
   DGS_REQUIRE(out_capacity == 0 || (coo_row != nullptr && coo_col != nullptr), DGS_ERR_INVALID,
               "dgs_sample_uniform: null output");
-  const PlanView pv = plan_view(const_cast<void*>(plan), n);
-  const uint64_t key = mix64(rng_seed) ^ mix64(rng_offset ^ 0xA5A5A5A55A5A5A5Aull);
-  rc = ids64 ? launch_uniform<int64_t>(*indices, seeds, n, k, replace != 0, pv, order, key, coo_row, coo_col,
-                                       out_capacity, picked_pos, status, s)
-             : launch_uniform<int32_t>(*indices, seeds, n, k, replace != 0, pv, order, key, coo_row, coo_col,
-                                       out_capacity, picked_pos, status, s);
+  rc = launch_sample_uniform(*indices, seeds, ids64 != 0, exact_count(n), k, replace != 0, const_cast<void*>(plan),
+                             order, sample_rng_key(rng_seed, rng_offset), coo_row, coo_col, out_capacity,
+                             picked_pos, false, status, s);
   if (rc != DGS_OK) return rc;
   if (nnz != nullptr) {
-    copy_total_kernel<<<1, 1, 0, s>>>(pv.total, nnz);
+    copy_total_kernel<<<1, 1, 0, s>>>(sample_plan_total(const_cast<void*>(plan), n), nnz);
     DGS_LAUNCH_CHECK();
   }
   return DGS_OK;
@@ -665,22 +715,12 @@ extern "C" int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chun
   }
   DGS_REQUIRE(out_capacity == 0 || (coo_row != nullptr && coo_col != nullptr), DGS_ERR_INVALID,
               "dgs_sample_weighted: null output");
-  const PlanView pv = plan_view(const_cast<void*>(plan), n);
-  const uint64_t key = mix64(rng_seed) ^ mix64(rng_offset ^ 0xA5A5A5A55A5A5A5Aull);
-  const unsigned grid = static_cast<unsigned>((n + SAMPLE_BLOCK / 32 - 1) / (SAMPLE_BLOCK / 32));
-  if (ids64)
-    sample_weighted_kernel<int64_t><<<grid, SAMPLE_BLOCK, 0, s>>>(
-        *indices, *probs, static_cast<const int64_t*>(seeds), n, k, replace != 0, pv.row_begin, pv.deg,
-        pv.local_off, pv.tile_off, order, key, static_cast<int64_t*>(coo_row), static_cast<int64_t*>(coo_col), out_capacity,
-        picked_pos, status);
-  else
-    sample_weighted_kernel<int32_t><<<grid, SAMPLE_BLOCK, 0, s>>>(
-        *indices, *probs, static_cast<const int32_t*>(seeds), n, k, replace != 0, pv.row_begin, pv.deg,
-        pv.local_off, pv.tile_off, order, key, static_cast<int32_t*>(coo_row), static_cast<int32_t*>(coo_col), out_capacity,
-        picked_pos, status);
-  DGS_LAUNCH_CHECK();
+  rc = launch_sample_weighted(*indices, *probs, seeds, ids64 != 0, exact_count(n), k, replace != 0,
+                              const_cast<void*>(plan), order, sample_rng_key(rng_seed, rng_offset), coo_row,
+                              coo_col, out_capacity, picked_pos, false, status, s);
+  if (rc != DGS_OK) return rc;
   if (nnz != nullptr) {
-    copy_total_kernel<<<1, 1, 0, s>>>(pv.total, nnz);
+    copy_total_kernel<<<1, 1, 0, s>>>(sample_plan_total(const_cast<void*>(plan), n), nnz);
     DGS_LAUNCH_CHECK();
   }
   return DGS_OK;

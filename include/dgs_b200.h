@@ -265,6 +265,53 @@ DGS_API int dgs_relabel_lookup(const void* table, size_t table_bytes, int64_t n_
                        const dgs_segments* in, int32_t ids64, void* out,
                        dgs_stream_t stream);
 
+/* ---- multi-hop sample + relabel, queued as one sequence ---------------- */
+/* Replaces the hop loop of ChunkTensorSampler.sample_blocks (reference
+ * oppo_bench/single_node/utils/chunktensor_sampler.py:93-118): for every fan-out,
+ * last one first as there, sample the current seeds, take the first-occurrence
+ * unique list of (seeds ++ sampled neighbours) as the next hop's seeds, and
+ * relabel the hop's COO into positions of that list -- what the reference does
+ * with one _CAPI_sample_neighbors* and one _CAPI_tensor_relabel call per hop,
+ * each with a blocking size read-back.  Here no size is read back while the
+ * sequence runs: buffers are sized by upper bounds (dgs_sample_blocks_bounds),
+ * every kernel takes its item count from a device word written by the kernel
+ * before it, and the actual sizes are written to `sizes` for one read at the end.
+ *
+ * hops[] is in the order of APPLICATION (hops[0] samples the caller's seeds).
+ * On return (after the stream reaches this point), for hop h:
+ *   sizes[2h]   = nnz_h: valid entries of coo_row / coo_col
+ *   sizes[2h+1] = valid entries of frontier (= number of seeds of hop h+1)
+ *   coo_row[e]  = index in frontier_h of the seed that edge e was sampled for
+ *                 (the seeds come first in frontier_h, in order, so for a
+ *                 duplicate-free seed list this is the seed's position)
+ *   coo_col[e]  = index of the sampled neighbour in frontier_h
+ * Results are the same as the per-hop operators give (same grouping by seed,
+ * whole rows in CSC order, first-occurrence numbering); stochastic rows use the
+ * random stream (rng_seed, rng_offset + h). */
+#define DGS_MAX_HOPS 8
+typedef struct dgs_hop {
+  int64_t fanout;
+  int64_t seed_bound;     /* capacity of this hop's seed list; hop 0: the exact number of seeds */
+  int64_t frontier_bound; /* capacity of `frontier`; equals seed_bound of the next hop */
+  void* coo_row;          /* [seed_bound * fanout] ids */
+  void* coo_col;          /* [seed_bound * fanout] ids */
+  void* frontier;         /* [frontier_bound] ids */
+} dgs_hop;
+
+/* Fills fanout / seed_bound / frontier_bound of hops[0..n_hops): hop h can reach
+ * at most seed_bound * (1 + fanout) distinct nodes and never more than num_nodes. */
+DGS_API int dgs_sample_blocks_bounds(int64_t n_seeds, const int64_t* fanouts, int32_t n_hops,
+                                     int64_t num_nodes, dgs_hop* hops);
+DGS_API size_t dgs_sample_blocks_workspace_bytes(const dgs_hop* hops, int32_t n_hops);
+/* probs == NULL: uniform sampling.  workspace: device memory, 16-byte aligned,
+ * contents irrelevant.  sizes: [2 * n_hops] int64, device-writable (pinned). */
+DGS_API int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_desc* indices,
+                              const dgs_chunk_desc* probs, const void* seeds, int32_t ids64,
+                              const dgs_hop* hops, int32_t n_hops, int32_t replace,
+                              uint64_t rng_seed, uint64_t rng_offset, void* workspace,
+                              size_t workspace_bytes, int64_t* sizes, int32_t* status,
+                              dgs_stream_t stream);
+
 /* ---- PaGraph-style feature cache ---------------------------------------- */
 /* CreateHashMapTensorCUDA, src/cuda/pagraph.cu:94-124: open-addressing table
  * key -> value with capacity dgs_cache_table_slots(n); key_buf/value_buf hold

@@ -96,3 +96,28 @@ def test_argument_errors_are_exceptions_not_exits(pkg):
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError):      # no GPU: loud failure, no CPU fallback
             torch.classes.dgs_classes.ChunkTensor([100], torch.int64, 200)
+
+
+def test_sample_blocks_bounds_and_workspace(abi, pkg):
+    """Host-only part of the multi-hop sequence: upper bounds per hop and the workspace they need."""
+    applied = (ctypes.c_int64 * 3)(5, 10, 15)
+    hops = (pkg.Hop * 3)()
+    assert abi.dgs_sample_blocks_bounds(1024, applied, 3, 2_449_029, hops) == 0
+    assert [(h.fanout, h.seed_bound, h.frontier_bound) for h in hops] == \
+        [(5, 1024, 6144), (10, 6144, 67584), (15, 67584, 1081344)]
+    ws = abi.dgs_sample_blocks_workspace_bytes(hops, 3)
+    expect = 256
+    for h in hops:
+        for b in (abi.dgs_sample_plan_bytes(h.seed_bound), abi.dgs_relabel_table_bytes(h.seed_bound * (1 + h.fanout))):
+            expect += -(-b // 256) * 256
+    assert ws == expect
+    # the node count caps a frontier; a seed list longer than the node list (repeats) keeps its own length
+    assert abi.dgs_sample_blocks_bounds(1024, applied, 3, 5000, hops) == 0
+    assert [h.frontier_bound for h in hops] == [5000, 5000, 5000]
+    assert abi.dgs_sample_blocks_bounds(8000, applied, 1, 5000, hops) == 0 and hops[0].frontier_bound == 8000
+    # refused, with a message: no fan-out, too many hops, a hop that could exceed 2^30 keys
+    assert abi.dgs_sample_blocks_bounds(10, applied, 0, 100, hops) != 0
+    assert abi.dgs_sample_blocks_bounds(10, (ctypes.c_int64 * 1)(0), 1, 100, hops) != 0
+    assert abi.dgs_sample_blocks_bounds(1 << 28, applied, 1, 1 << 40, hops) != 0
+    assert b"keys" in abi.dgs_last_error()
+    assert abi.dgs_sample_blocks_workspace_bytes(None, 3) == 0
