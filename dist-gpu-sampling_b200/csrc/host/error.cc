@@ -3,6 +3,7 @@
 // src/dgs_headers.h:11-45): failures are returned to the caller as codes.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "../kernels/common.cuh"
 
@@ -16,6 +17,15 @@ void set_error(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
+}
+
+// DGS_NO_PDL=1 launches every kernel the plain way (no programmatic stream serialization)
+bool chained_launches_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("DGS_NO_PDL");
+    return !(e != nullptr && e[0] == '1');
+  }();
+  return on;
 }
 
 int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {

@@ -35,6 +35,7 @@ struct InitWords {
 };
 
 __global__ void blocks_init_kernel(const InitWords w) {
+  pdl_enter();
   if (threadIdx.x == 0) *w.n0 = w.n0_value;
   if (threadIdx.x < w.n_tickets) *w.tickets[threadIdx.x] = 0u;
 }
@@ -151,8 +152,7 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
     init.tickets[init.n_tickets++] = sample_plan_ticket(plan[h], hops[h].seed_bound);
     init.tickets[init.n_tickets++] = unique_ticket(table[h], key_bound);
   }
-  blocks_init_kernel<<<1, 32, 0, s>>>(init);
-  DGS_LAUNCH_CHECK();
+  DGS_CUDA_TRY(launch_chained(blocks_init_kernel, 1u, 32u, s, init));
 
   // ---- queue every hop; no size is read back in between ----
   const void* hop_seeds = seeds;

@@ -60,6 +60,36 @@ static inline Count exact_count(int64_t n) { return Count{n, nullptr, nullptr}; 
 
 constexpr unsigned FULL_MASK = 0xffffffffu;
 
+// ---- chained launches ----------------------------------------------------------
+// Kernels that follow one another on a stream are launched with programmatic
+// stream serialization: the next kernel's CTAs may be placed on the SMs while the
+// previous kernel drains, which takes the launch latency out of a chain of short
+// dependent kernels.  Every such kernel starts with pdl_enter(): it waits until
+// the previous kernel has completed and its writes are visible (so nothing about
+// the data flow changes) and then lets its own successor be placed.
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+bool chained_launches_enabled();  // false with DGS_NO_PDL=1 (host/error.cc)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t s,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launches_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ int64_t count_of(const Count& c) {
   if (c.dev == nullptr) return c.bound;
   int64_t v = *c.dev;

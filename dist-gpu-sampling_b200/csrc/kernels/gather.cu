@@ -138,6 +138,7 @@ gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int6
   using V = typename VecT<VEC>::type;
   __shared__ const char* s_src[GATHER_MAX_ROWS];
   __shared__ char* s_dst[GATHER_MAX_ROWS];  // only used with a processing order
+  pdl_enter();
 
   const int64_t tile_row0 = static_cast<int64_t>(blockIdx.x) * rows_per_tile;
   const uint32_t rows_here =
@@ -237,9 +238,8 @@ int launch_gather(const Src& rows, int64_t n, int64_t D, int sh, void* out, cons
       nvec == 1 ? 0u : static_cast<uint32_t>(((1ull << 32) + nvec - 1) / nvec);
   const int64_t tiles = (n + rows_per_tile - 1) / rows_per_tile;
   DGS_REQUIRE(tiles <= 0x7fffffffLL, DGS_ERR_UNSUPPORTED, "gather: too many rows (%lld)", (long long)n);
-  gather_rows_kernel<Src, VEC><<<static_cast<unsigned>(tiles), GATHER_BLOCK, 0, stream>>>(
-      rows, n, D, sh, nvec, rows_per_tile, magic, static_cast<char*>(out), order, status);
-  DGS_LAUNCH_CHECK();
+  DGS_CUDA_TRY(launch_chained(gather_rows_kernel<Src, VEC>, static_cast<unsigned>(tiles), GATHER_BLOCK, stream, rows,
+                              n, D, sh, nvec, rows_per_tile, magic, static_cast<char*>(out), order, status));
   return DGS_OK;
 }
 

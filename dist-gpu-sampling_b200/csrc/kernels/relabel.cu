@@ -118,6 +118,7 @@ struct PairKeys {
 // key count will use (the per-operator path clears with a memset instead)
 __global__ void __launch_bounds__(RL_BLOCK)
 relabel_clear_kernel(Slot* __restrict__ slots, const Count n_keys) {
+  pdl_enter();
   const uint64_t cap = slots_for(count_of(n_keys));
   const uint64_t i = static_cast<uint64_t>(blockIdx.x) * (RL_BLOCK * 4) + threadIdx.x;
   const ulonglong2 empty = make_ulonglong2(~0ull, ~0ull);
@@ -133,6 +134,7 @@ template <typename IdT, typename Keys>
 __global__ void __launch_bounds__(RL_BLOCK)
 relabel_insert_kernel(const __grid_constant__ Keys keys, Slot* slots, uint32_t* __restrict__ slot_of,
                       int32_t* __restrict__ status) {
+  pdl_enter();
   const int64_t n = keys.size();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
   if (i >= n) return;
@@ -176,6 +178,7 @@ relabel_count_kernel(const Count nc, const Slot* __restrict__ slots,
                      int64_t* total_dev, int64_t* n_unique_out) {
   __shared__ int s_cnt;
   __shared__ int64_t s_scan[RL_BLOCK / 32 + 1];
+  pdl_enter();
   if (threadIdx.x == 0) s_cnt = 0;
   __syncthreads();
   const int64_t n = count_of(nc);
@@ -204,6 +207,7 @@ relabel_number_kernel(const __grid_constant__ Keys keys, Slot* slots, const uint
                       const int64_t* __restrict__ tile_off, IdT* __restrict__ unique_out,
                       const int64_t unique_capacity, int32_t* __restrict__ status) {
   __shared__ int smem[RL_BLOCK / 32 + 1];
+  pdl_enter();
   const int64_t n = keys.size();
   const int64_t base = static_cast<int64_t>(blockIdx.x) * RL_TILE + threadIdx.x * RL_ITEMS;
   bool first[RL_ITEMS];
@@ -254,6 +258,7 @@ template <typename IdT>
 __global__ void __launch_bounds__(RL_BLOCK)
 relabel_lookup_kernel(const __grid_constant__ dgs_segments in, const int64_t n,
                       const Slot* __restrict__ slots, const uint64_t mask, IdT* __restrict__ out) {
+  pdl_enter();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
   if (i >= n) return;
   out[i] = static_cast<IdT>(probe_label(slots, mask, static_cast<long long>(seg_load<IdT>(in, i))));
@@ -266,6 +271,7 @@ template <typename IdT>
 __global__ void __launch_bounds__(RL_BLOCK)
 relabel_lookup_pair_kernel(const IdT* a, const IdT* b, const Count nc, const Count n_keys,
                            const Slot* __restrict__ slots, IdT* out_a, IdT* out_b) {
+  pdl_enter();
   const int64_t n = count_of(nc);
   const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
   if (i >= n) return;
@@ -296,14 +302,12 @@ template <typename IdT, typename Keys>
 int run_unique(const Keys& keys, Count n_keys, const TableView& t, void* unique_out, int64_t unique_capacity,
                int64_t* n_unique, int32_t* status, cudaStream_t s) {
   const unsigned per_key_grid = static_cast<unsigned>((n_keys.bound + RL_BLOCK - 1) / RL_BLOCK);
-  relabel_insert_kernel<IdT, Keys><<<per_key_grid, RL_BLOCK, 0, s>>>(keys, t.slots, t.slot_of, status);
-  DGS_LAUNCH_CHECK();
-  relabel_count_kernel<<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(n_keys, t.slots, t.slot_of, t.tile_off,
-                                                                            t.ticket, t.total, n_unique);
-  DGS_LAUNCH_CHECK();
-  relabel_number_kernel<IdT, Keys><<<static_cast<unsigned>(t.ntiles), RL_BLOCK, 0, s>>>(
-      keys, t.slots, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out), unique_capacity, status);
-  DGS_LAUNCH_CHECK();
+  DGS_CUDA_TRY(launch_chained(relabel_insert_kernel<IdT, Keys>, per_key_grid, RL_BLOCK, s, keys, t.slots, t.slot_of,
+                              status));
+  DGS_CUDA_TRY(launch_chained(relabel_count_kernel, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, n_keys, t.slots,
+                              t.slot_of, t.tile_off, t.ticket, t.total, n_unique));
+  DGS_CUDA_TRY(launch_chained(relabel_number_kernel<IdT, Keys>, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, keys,
+                              t.slots, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out), unique_capacity, status));
   return DGS_OK;
 }
 
@@ -323,9 +327,8 @@ int launch_unique_pair(bool ids64, const void* a, Count na, const void* b, Count
               "relabel: the pair form takes one device word per length");
   const PairKeys keys{a, b, na, nb};
   const uint64_t cap = slots_for(key_bound);
-  relabel_clear_kernel<<<static_cast<unsigned>((cap + RL_BLOCK * 4 - 1) / (RL_BLOCK * 4)), RL_BLOCK, 0, s>>>(t.slots,
-                                                                                                          n_keys);
-  DGS_LAUNCH_CHECK();
+  DGS_CUDA_TRY(launch_chained(relabel_clear_kernel, static_cast<unsigned>((cap + RL_BLOCK * 4 - 1) / (RL_BLOCK * 4)),
+                              RL_BLOCK, s, t.slots, n_keys));
   return ids64 ? run_unique<int64_t, PairKeys>(keys, n_keys, t, unique_out, unique_capacity, n_unique_out, status, s)
                : run_unique<int32_t, PairKeys>(keys, n_keys, t, unique_out, unique_capacity, n_unique_out, status, s);
 }
@@ -336,14 +339,13 @@ int launch_lookup_pair(const void* table, int64_t key_bound, Count n_keys, bool 
   const TableView t = table_view(const_cast<void*>(table), key_bound);
   const unsigned grid = static_cast<unsigned>((n.bound + RL_BLOCK - 1) / RL_BLOCK);
   if (ids64)
-    relabel_lookup_pair_kernel<int64_t><<<grid, RL_BLOCK, 0, s>>>(
-        static_cast<const int64_t*>(a), static_cast<const int64_t*>(b), n, n_keys, t.slots,
-        static_cast<int64_t*>(out_a), static_cast<int64_t*>(out_b));
+    DGS_CUDA_TRY(launch_chained(relabel_lookup_pair_kernel<int64_t>, grid, RL_BLOCK, s, static_cast<const int64_t*>(a),
+                                static_cast<const int64_t*>(b), n, n_keys, t.slots, static_cast<int64_t*>(out_a),
+                                static_cast<int64_t*>(out_b)));
   else
-    relabel_lookup_pair_kernel<int32_t><<<grid, RL_BLOCK, 0, s>>>(
-        static_cast<const int32_t*>(a), static_cast<const int32_t*>(b), n, n_keys, t.slots,
-        static_cast<int32_t*>(out_a), static_cast<int32_t*>(out_b));
-  DGS_LAUNCH_CHECK();
+    DGS_CUDA_TRY(launch_chained(relabel_lookup_pair_kernel<int32_t>, grid, RL_BLOCK, s, static_cast<const int32_t*>(a),
+                                static_cast<const int32_t*>(b), n, n_keys, t.slots, static_cast<int32_t*>(out_a),
+                                static_cast<int32_t*>(out_b)));
   return DGS_OK;
 }
 
@@ -404,9 +406,10 @@ extern "C" int dgs_relabel_lookup(const void* table, size_t table_bytes, int64_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>((n + RL_BLOCK - 1) / RL_BLOCK);
   if (ids64)
-    relabel_lookup_kernel<int64_t><<<grid, RL_BLOCK, 0, s>>>(*in, n, t.slots, t.cap - 1, static_cast<int64_t*>(out));
+    DGS_CUDA_TRY(launch_chained(relabel_lookup_kernel<int64_t>, grid, RL_BLOCK, s, *in, n, t.slots, t.cap - 1,
+                                static_cast<int64_t*>(out)));
   else
-    relabel_lookup_kernel<int32_t><<<grid, RL_BLOCK, 0, s>>>(*in, n, t.slots, t.cap - 1, static_cast<int32_t*>(out));
-  DGS_LAUNCH_CHECK();
+    DGS_CUDA_TRY(launch_chained(relabel_lookup_kernel<int32_t>, grid, RL_BLOCK, s, *in, n, t.slots, t.cap - 1,
+                                static_cast<int32_t*>(out)));
   return DGS_OK;
 }

@@ -98,6 +98,7 @@ sample_plan_kernel(const __grid_constant__ dgs_chunk_desc indptr, const IdT* __r
                    unsigned int* ticket, int64_t* nnz_out, int32_t* __restrict__ status) {
   __shared__ int64_t smem[SAMPLE_BLOCK / 32 + 1];
   constexpr int sh = sizeof(IdT) == 8 ? 3 : 2;
+  pdl_enter();
   const int64_t n = count_of(nc);
   const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + threadIdx.x;
   int64_t cnt = 0;
@@ -182,7 +183,7 @@ __device__ __forceinline__ SeedPlan seed_plan(const int64_t* __restrict__ plan_r
 // uniform sampling: G lanes per seed
 // ---------------------------------------------------------------------------
 template <typename IdT, int G>
-__global__ void __launch_bounds__(SAMPLE_BLOCK)
+__global__ void __launch_bounds__(SAMPLE_BLOCK, 6)
 sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT* __restrict__ seeds,
                       const Count nc, const int64_t k, const bool replace,
                       const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
@@ -191,8 +192,11 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
                       const int64_t out_capacity, int64_t* __restrict__ picked_pos,
                       const bool row_is_position, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
+  pdl_enter();
   const int64_t n = count_of(nc);
   constexpr int GROUPS = SAMPLE_BLOCK / G;  // seeds per CTA
+  constexpr int TAKEN_WORDS = 4096;         // 16 KB of position bitmaps per CTA, split between its groups
+  __shared__ uint32_t s_taken[TAKEN_WORDS];
   const int lane = threadIdx.x & 31;
   const int l = threadIdx.x % G;        // lane inside the group
   const int group = threadIdx.x / G;    // group inside the CTA
@@ -221,10 +225,20 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
 
     if (fast) {
       // -- distinct positions by parallel rejection (all 32 lanes take part) --
+      // Every lane of a group draws a position and marks it in the group's bitmap
+      // in shared memory; a lane that finds its bit already set draws again.  Only
+      // equality of positions matters, so every k-subset is equally likely.
+      constexpr int WORDS = TAKEN_WORDS / GROUPS;         // bitmap words per group
+      constexpr int64_t MAP_DEG = static_cast<int64_t>(WORDS) * 32;
+      uint32_t* taken = s_taken + group * WORDS;
       const bool sampled = valid && deg > k;
       const bool complement = sampled && 2 * k > deg;  // draw the deg-k positions to leave out
       const int64_t m = sampled ? (complement ? deg - k : k) : 0;
       const bool active = l < m;
+      const bool in_map = deg <= MAP_DEG;              // longer rows compare candidates across the warp
+      if (sampled && in_map)
+        for (int wd = l; wd < static_cast<int>((deg + 31) >> 5); wd += G) taken[wd] = 0u;
+      __syncwarp();
       bool need = active;
       int64_t c = 0;
       const bool small_row = deg <= 0xFFFFFFFFll;  // every real graph; longer rows take the general path
@@ -247,33 +261,38 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
             const Philox4 r = philox4x32_10(key, i_lo, i_hi, (round << 8) | static_cast<uint32_t>(l), TAG_UNIFORM ^ 1u);
             c = static_cast<int64_t>(bounded(r, static_cast<uint64_t>(deg)));
           }
+          if (in_map && usable) {
+            const uint32_t bit = 1u << (static_cast<uint32_t>(c) & 31u);
+            need = (atomicOr(&taken[c >> 5], bit) & bit) != 0u;
+          }
         }
-        // lanes holding the same position inside one group see each other; the lowest keeps it
-        const unsigned long long tag =
-            (active && usable) ? (static_cast<unsigned long long>(c) | (static_cast<unsigned long long>(gw) << 58))
+        if (__any_sync(FULL_MASK, active && !in_map)) {
+          // lanes holding the same position inside one group see each other; the lowest keeps it
+          const bool mine = active && !in_map;
+          const unsigned long long tag =
+              (mine && usable) ? (static_cast<unsigned long long>(c) | (static_cast<unsigned long long>(gw) << 58))
                                : (0x8000000000000000ull | static_cast<unsigned long long>(lane));
-        const unsigned same = __match_any_sync(FULL_MASK, tag);
-        need = active && (!usable || (__ffs(same) - 1 != lane));
+          const unsigned same = __match_any_sync(FULL_MASK, tag);
+          if (mine) need = !usable || (__ffs(same) - 1 != lane);
+        }
         if (round >= 64 + 1024) {
           if (need) raise_status(status, DGS_ERR_TABLE_FULL);
           break;
         }
       }
-      if (__any_sync(FULL_MASK, complement)) {
-        // the row has at most 2k-1 <= 63 positions: OR the left-out positions of the
-        // group into one 64-bit mask, then every lane ranks its own two positions
-        // (a = l and b = l + G cover the row) among the kept ones -- no shuffles
-        const unsigned long long bit = (complement && active) ? (1ull << c) : 0ull;
+      __syncwarp();
+      if (complement) {
+        // the row has at most 2k-1 <= 63 positions, so its bitmap is one or two words:
+        // every lane ranks its own two positions (a = l and b = l + G cover the row)
+        // among the kept ones
         const unsigned long long out_mask =
-            static_cast<unsigned long long>(__reduce_or_sync(gmask, static_cast<unsigned>(bit))) |
-            (static_cast<unsigned long long>(__reduce_or_sync(gmask, static_cast<unsigned>(bit >> 32))) << 32);
-        if (complement) {
-          const unsigned long long row_mask = (1ull << deg) - 1ull;  // deg <= 63
-          const unsigned long long kept = ~out_mask & row_mask;
-          const int a = l, b = l + G;
-          if ((kept >> a) & 1ull) emit(o, __popcll(kept & ((1ull << a) - 1ull)), seed, rb, a);
-          if (b < 64 && ((kept >> b) & 1ull)) emit(o, __popcll(kept & ((1ull << b) - 1ull)), seed, rb, b);
-        }
+            static_cast<unsigned long long>(taken[0]) |
+            (deg > 32 ? static_cast<unsigned long long>(taken[1]) << 32 : 0ull);
+        const unsigned long long row_mask = (1ull << deg) - 1ull;  // deg <= 63
+        const unsigned long long kept = ~out_mask & row_mask;
+        const int a = l, b = l + G;
+        if ((kept >> a) & 1ull) emit(o, __popcll(kept & ((1ull << a) - 1ull)), seed, rb, a);
+        if (b < 64 && ((kept >> b) & 1ull)) emit(o, __popcll(kept & ((1ull << b) - 1ull)), seed, rb, b);
       }
       if (sampled && !complement) {
         if (active) emit(o, l, seed, rb, c);
@@ -407,6 +426,7 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
                        const int64_t out_capacity, int64_t* __restrict__ picked_pos,
                        const bool row_is_position, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
+  pdl_enter();
   const int64_t n = count_of(nc);
   const int l = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -545,10 +565,9 @@ int check_sample_args(const char* who, const void* seeds, int64_t n, int64_t k, 
 template <typename IdT>
 int plan_typed(const dgs_chunk_desc& indptr, const void* seeds, Count n, int64_t k, bool replace,
                const PlanView& pv, int64_t* nnz, int32_t* status, cudaStream_t s) {
-  sample_plan_kernel<IdT><<<static_cast<unsigned>(pv.ntiles), SAMPLE_BLOCK, 0, s>>>(
-      indptr, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
-      pv.tile_off, pv.total, pv.ticket, nnz, status);
-  DGS_LAUNCH_CHECK();
+  DGS_CUDA_TRY(launch_chained(sample_plan_kernel<IdT>, static_cast<unsigned>(pv.ntiles), SAMPLE_BLOCK, s, indptr,
+                              static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
+                              pv.tile_off, pv.total, pv.ticket, nnz, status));
   return DGS_OK;
 }
 
@@ -556,18 +575,17 @@ template <typename IdT>
 int uniform_typed(const dgs_chunk_desc& indices, const void* seeds, Count n, int64_t k, bool replace,
                   const PlanView& pv, const uint32_t* order, uint64_t key, void* coo_row, void* coo_col,
                   int64_t cap, int64_t* pos, bool rowpos, int32_t* status, cudaStream_t s) {
-#define DGS_LAUNCH_U(G)                                                                                  \
-  sample_uniform_kernel<IdT, G>                                                                          \
-      <<<static_cast<unsigned>((n.bound + SAMPLE_BLOCK / G - 1) / (SAMPLE_BLOCK / G)), SAMPLE_BLOCK, 0, s>>>( \
-          indices, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,    \
-          pv.tile_off, order, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, rowpos, \
-          status)
+#define DGS_LAUNCH_U(G)                                                                                      \
+  DGS_CUDA_TRY(launch_chained(sample_uniform_kernel<IdT, G>,                                                 \
+                              static_cast<unsigned>((n.bound + SAMPLE_BLOCK / G - 1) / (SAMPLE_BLOCK / G)),  \
+                              SAMPLE_BLOCK, s, indices, static_cast<const IdT*>(seeds), n, k, replace,       \
+                              pv.row_begin, pv.deg, pv.local_off, pv.tile_off, order, key,                   \
+                              static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, rowpos, status))
   if (k <= 4) DGS_LAUNCH_U(4);
   else if (k <= 8) DGS_LAUNCH_U(8);
   else if (k <= 16) DGS_LAUNCH_U(16);
   else DGS_LAUNCH_U(32);
 #undef DGS_LAUNCH_U
-  DGS_LAUNCH_CHECK();
   return DGS_OK;
 }
 
@@ -577,10 +595,10 @@ int weighted_typed(const dgs_chunk_desc& indices, const dgs_chunk_desc& probs, c
                    void* coo_row, void* coo_col, int64_t cap, int64_t* pos, bool rowpos, int32_t* status,
                    cudaStream_t s) {
   const unsigned grid = static_cast<unsigned>((n.bound + SAMPLE_BLOCK / 32 - 1) / (SAMPLE_BLOCK / 32));
-  sample_weighted_kernel<IdT><<<grid, SAMPLE_BLOCK, 0, s>>>(
-      indices, probs, static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
-      pv.tile_off, order, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, rowpos, status);
-  DGS_LAUNCH_CHECK();
+  DGS_CUDA_TRY(launch_chained(sample_weighted_kernel<IdT>, grid, SAMPLE_BLOCK, s, indices, probs,
+                              static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
+                              pv.tile_off, order, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap,
+                              pos, rowpos, status));
   return DGS_OK;
 }
 
