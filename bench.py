@@ -71,7 +71,8 @@ def workload(args):
 LAUNCHES_SAMPLE = 2   # plan (+ tile scan in its last CTA), sample
 LAUNCHES_RELABEL = 4  # insert, count (+ tile scan in its last CTA), number, lookup
 LAUNCHES_GATHER = 1
-LAUNCHES_HOP_FUSED = 7  # plan, sample, clear, insert, count, number, lookup (+ 1 init kernel per step)
+LAUNCHES_HOP_FUSED = 5  # plan (+ table clear + previous hop's lookup), sample, insert, count, number
+LAUNCHES_STEP_FUSED = 2  # init words, last hop's lookup
 # DRAM bytes per gathered row (read + write) from the ncu capture summarised in
 # profiles/; None until a capture exists for the benchmarked row width
 NCU_TRAFFIC_BYTES_PER_ROW = {100: 860.7}
@@ -442,7 +443,7 @@ def main_ours(args):
                           "gather_payload_gbs_all_ranks": rows_all * dim * 4 / (gather_ms * 1e-3) / 1e9},
             "e2e": {"value": e2e_edges_all / (e2e_ms * 1e-3), "unit": "edges/s",
                     "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * ((1 + len(fanouts) * LAUNCHES_HOP_FUSED if args.fused else
+            "gpu_launches": args.steps * ((LAUNCHES_STEP_FUSED + len(fanouts) * LAUNCHES_HOP_FUSED if args.fused else
                                            len(fanouts) * (LAUNCHES_SAMPLE + LAUNCHES_RELABEL)) + LAUNCHES_GATHER),
             "api": "_CAPI_sample_blocks* (all hops queued as one sequence)" if args.fused
                    else "reference operator sequence: _CAPI_sample_neighbors* + _CAPI_tensor_relabel per hop",

@@ -35,6 +35,7 @@ HEADERS = [
     "kernels/philox.cuh",
     "kernels/tile_scan.cuh",
     "kernels/launchers.h",
+    "kernels/relabel_device.cuh",
     "host/comm.h",
     "../../include/dgs_b200.h",
 ]

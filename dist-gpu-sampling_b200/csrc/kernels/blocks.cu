@@ -14,10 +14,13 @@
 // than the graph has), and the actual sizes go to a caller-supplied (pinned)
 // array that the host reads once, after everything is queued.
 //
-// Per hop: plan -> sample -> clear table -> insert -> count -> number -> lookup.
-// From the second hop on the seed list is a relabel's unique list, so a seed's
-// relabelled id is its position and the sampler writes that directly; only the
-// first hop (whose seeds the caller may repeat) looks its rows up.
+// Per hop: plan -> sample -> insert -> count -> number; the plan launch also
+// carries, as extra CTAs, two jobs that depend on nothing it does: clearing the
+// table this hop will fill and relabelling the COO of the hop before (whose
+// numbering is complete by then).  The last hop's COO is relabelled by a launch
+// of its own.  From the second hop on the seed list is a relabel's unique list,
+// so a seed's relabelled id is its position and the sampler writes that directly;
+// only the first hop (whose seeds the caller may repeat) looks its rows up.
 #include "common.cuh"
 #include "launchers.h"
 
@@ -157,14 +160,17 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
   // ---- queue every hop; no size is read back in between ----
   const void* hop_seeds = seeds;
   const int64_t* n_dev = n0_dev;
+  LookupJob pending{};  // relabelling of the previous hop's COO, carried by the next plan launch
   for (int h = 0; h < n_hops; ++h) {
     const dgs_hop& hp = hops[h];
     const int64_t k = hp.fanout;
     const int64_t edge_bound = hp.seed_bound * k;
     const int64_t key_bound = hp.seed_bound + edge_bound;
     const Count n{hp.seed_bound, n_dev, nullptr};
+    // the table is dimensioned before the neighbours are drawn: seeds * (1 + fanout) keys at most
+    const TableSize size{n, 1 + k};
     rc = launch_sample_plan(*indptr, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], &sizes[2 * h], false,
-                            status, s);
+                            make_clear_job(table[h], key_bound, size), pending, status, s);
     if (rc != DGS_OK) return rc;
     const int64_t* nnz_dev = sample_plan_total(plan[h], hp.seed_bound);
     const uint64_t key = sample_rng_key(rng_seed, rng_offset + static_cast<uint64_t>(h));
@@ -176,15 +182,13 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
                                      hp.coo_row, hp.coo_col, edge_bound, nullptr, row_is_position, status, s);
     if (rc != DGS_OK) return rc;
     const Count nnz{edge_bound, nnz_dev, nullptr};
-    rc = launch_unique_pair(ids64 != 0, hop_seeds, n, hp.coo_col, nnz, key_bound, table[h], hp.frontier,
+    rc = launch_unique_pair(ids64 != 0, hop_seeds, n, hp.coo_col, nnz, key_bound, size, table[h], hp.frontier,
                             hp.frontier_bound, &sizes[2 * h + 1], status, s);
     if (rc != DGS_OK) return rc;
-    const Count n_keys{key_bound, n_dev, nnz_dev};
-    rc = launch_lookup_pair(table[h], key_bound, n_keys, ids64 != 0, row_is_position ? nullptr : hp.coo_row,
-                            hp.coo_col, nnz, hp.coo_row, hp.coo_col, s);
-    if (rc != DGS_OK) return rc;
+    pending = make_lookup_job(table[h], key_bound, size, row_is_position ? nullptr : hp.coo_row, hp.coo_col, nnz,
+                              hp.coo_row, hp.coo_col);
     hop_seeds = hp.frontier;
     n_dev = unique_total(table[h], key_bound);
   }
-  return DGS_OK;
+  return launch_lookup(pending, ids64 != 0, s);
 }

@@ -2,6 +2,7 @@
 // relabel.cu) and the multi-hop sequence (blocks.cu).  Not part of the C ABI.
 #pragma once
 #include "common.cuh"
+#include "relabel_device.cuh"
 
 namespace dgs {
 
@@ -10,9 +11,12 @@ namespace dgs {
 // receives the number of sampled edges; the same number stays in the plan at
 // sample_plan_total().  The plan's ticket word must be zero at launch: it is
 // cleared here when zero_ticket is set and resets itself after every use.
+// clear / lookup (either may have ctas == 0): independent jobs run by extra CTAs of
+// the plan launch -- clearing the table this hop will fill, relabelling the COO of
+// the hop before it.
 int launch_sample_plan(const dgs_chunk_desc& indptr, const void* seeds, bool ids64, Count n, int64_t k,
-                       bool replace, void* plan, int64_t* nnz_out, bool zero_ticket, int32_t* status,
-                       cudaStream_t s);
+                       bool replace, void* plan, int64_t* nnz_out, bool zero_ticket, const ClearJob& clear,
+                       const LookupJob& lookup, int32_t* status, cudaStream_t s);
 int64_t* sample_plan_total(void* plan, int64_t n_bound);
 unsigned int* sample_plan_ticket(void* plan, int64_t n_bound);
 
@@ -29,21 +33,23 @@ int launch_sample_weighted(const dgs_chunk_desc& indices, const dgs_chunk_desc& 
 uint64_t sample_rng_key(uint64_t rng_seed, uint64_t rng_offset);
 
 // ---- relabel.cu ----------------------------------------------------------------
+// `table` is laid out for key_bound keys (dgs_relabel_table_bytes(key_bound)); `size`
+// says how much of it is in use (cleared, probed); every kernel of one table gets
+// the same TableSize.
+ClearJob make_clear_job(void* table, int64_t key_bound, const TableSize& size);
+LookupJob make_lookup_job(const void* table, int64_t key_bound, const TableSize& size, const void* a, const void* b,
+                          Count n, void* out_a, void* out_b);
+int launch_clear(const ClearJob& job, cudaStream_t s);            // as a launch of its own
+int launch_lookup(const LookupJob& job, bool ids64, cudaStream_t s);
+
 // First-occurrence unique of the logical concatenation a[0:na) ++ b[0:nb) whose
-// lengths may be device words.  `table` is laid out for key_bound keys
-// (dgs_relabel_table_bytes(key_bound)); only the part of it that the actual key
-// count needs is cleared and probed.  unique_out holds unique_capacity ids; a
-// larger result raises DGS_ERR_RANGE in the status word and is cut off.  The
-// table's ticket word must be zero at launch (it resets itself after use).
+// lengths are device words, into a table that has been cleared.  unique_out holds
+// unique_capacity ids; a larger result raises DGS_ERR_RANGE in the status word and
+// is cut off.  The table's ticket word must be zero at launch (it resets itself).
 int launch_unique_pair(bool ids64, const void* a, Count na, const void* b, Count nb, int64_t key_bound,
-                       void* table, void* unique_out, int64_t unique_capacity, int64_t* n_unique_out,
-                       int32_t* status, cudaStream_t s);
+                       const TableSize& size, void* table, void* unique_out, int64_t unique_capacity,
+                       int64_t* n_unique_out, int32_t* status, cudaStream_t s);
 int64_t* unique_total(void* table, int64_t key_bound);
 unsigned int* unique_ticket(void* table, int64_t key_bound);
-
-// out_a[i] = label(a[i]) (skipped when a == nullptr), out_b[i] = label(b[i]), i < n.
-// n_keys: the key count the table was built with (same Count as na + nb above).
-int launch_lookup_pair(const void* table, int64_t key_bound, Count n_keys, bool ids64, const void* a,
-                       const void* b, Count n, void* out_a, void* out_b, cudaStream_t s);
 
 }  // namespace dgs

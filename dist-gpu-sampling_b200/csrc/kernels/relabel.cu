@@ -24,23 +24,15 @@
 //   * the number of distinct keys goes to a caller-supplied (pinned) word.
 #include "common.cuh"
 #include "launchers.h"
+#include "relabel_device.cuh"
 #include "philox.cuh"
 #include "tile_scan.cuh"
 
 namespace dgs {
 namespace {
 
-constexpr int RL_BLOCK = 256;
 constexpr int RL_ITEMS = 4;
 constexpr int RL_TILE = RL_BLOCK * RL_ITEMS;
-constexpr unsigned long long LABEL_BIT = 0x8000000000000000ull;
-constexpr long long EMPTY_KEY = -1;  // memset 0xFF: key = -1, value = 2^64-1
-constexpr uint32_t NO_SLOT = 0xFFFFFFFFu;
-
-struct __align__(16) Slot {
-  long long key;
-  unsigned long long val;
-};
 
 struct TableView {
   Slot* slots;         // [cap]
@@ -51,19 +43,6 @@ struct TableView {
   uint64_t cap;
   int64_t ntiles;
 };
-
-// slots in use for a table built from n keys: the power of two >= max(2n, 64)
-__host__ __device__ __forceinline__ uint64_t slots_for(int64_t n) {
-  uint64_t want = 2 * static_cast<uint64_t>(n);
-  if (want < 64) want = 64;
-#ifdef __CUDA_ARCH__
-  return 1ull << (64 - __clzll(static_cast<long long>(want - 1)));
-#else
-  uint64_t cap = 64;
-  while (cap < want) cap <<= 1;
-  return cap;
-#endif
-}
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -80,13 +59,6 @@ inline TableView table_view(void* mem, int64_t n) {
   t.total = t.tile_off + t.ntiles;
   t.ticket = reinterpret_cast<unsigned int*>(t.total + 1);
   return t;
-}
-
-__device__ __forceinline__ uint64_t hash_key(long long key) {
-  uint64_t z = static_cast<uint64_t>(key);
-  z = (z ^ (z >> 33)) * 0xFF51AFD7ED558CCDull;
-  z = (z ^ (z >> 33)) * 0xC4CEB9FE1A85EC53ull;
-  return z ^ (z >> 33);
 }
 
 // ---- where the keys come from ---------------------------------------------------
@@ -114,31 +86,24 @@ struct PairKeys {
   }
 };
 
-// pass 0 of the sequence with device-side counts: clear only the slots the actual
-// key count will use (the per-operator path clears with a memset instead)
-__global__ void __launch_bounds__(RL_BLOCK)
-relabel_clear_kernel(Slot* __restrict__ slots, const Count n_keys) {
+// pass 0 of the sequence with device-side counts, when it does not ride on another
+// launch: clear only the slots the table will use (the per-operator path clears
+// with a memset instead)
+__global__ void __launch_bounds__(RL_BLOCK) relabel_clear_kernel(const ClearJob job) {
   pdl_enter();
-  const uint64_t cap = slots_for(count_of(n_keys));
-  const uint64_t i = static_cast<uint64_t>(blockIdx.x) * (RL_BLOCK * 4) + threadIdx.x;
-  const ulonglong2 empty = make_ulonglong2(~0ull, ~0ull);
-#pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    const uint64_t at = i + static_cast<uint64_t>(u) * RL_BLOCK;
-    if (at < cap) *reinterpret_cast<ulonglong2*>(&slots[at]) = empty;
-  }
+  run_clear_cta(job, blockIdx.x);
 }
 
 // pass 1: insert every key, keep the smallest input index per key
 template <typename IdT, typename Keys>
 __global__ void __launch_bounds__(RL_BLOCK)
-relabel_insert_kernel(const __grid_constant__ Keys keys, Slot* slots, uint32_t* __restrict__ slot_of,
-                      int32_t* __restrict__ status) {
+relabel_insert_kernel(const __grid_constant__ Keys keys, const TableSize size, Slot* slots,
+                      uint32_t* __restrict__ slot_of, int32_t* __restrict__ status) {
   pdl_enter();
   const int64_t n = keys.size();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
   if (i >= n) return;
-  const uint64_t mask = slots_for(n) - 1;
+  const uint64_t mask = table_slots(size) - 1;
   const long long key = static_cast<long long>(keys.template load<IdT>(i));
   if (key < 0) {
     raise_status(status, DGS_ERR_RANGE);
@@ -241,18 +206,6 @@ relabel_number_kernel(const __grid_constant__ Keys keys, Slot* slots, const uint
   }
 }
 
-__device__ __forceinline__ long long probe_label(const Slot* __restrict__ slots, uint64_t mask, long long key) {
-  if (key < 0) return -1;
-  uint64_t h = hash_key(key) & mask;
-  for (uint64_t probes = 0; probes <= mask; ++probes) {
-    const Slot s = slots[h];  // one 16-byte load
-    if (s.key == key) return static_cast<long long>(s.val & ~LABEL_BIT);
-    if (s.key == EMPTY_KEY) break;
-    h = (h + 1) & mask;
-  }
-  return -1;
-}
-
 // lookup: label of each id, -1 when absent
 template <typename IdT>
 __global__ void __launch_bounds__(RL_BLOCK)
@@ -264,20 +217,11 @@ relabel_lookup_kernel(const __grid_constant__ dgs_segments in, const int64_t n,
   out[i] = static_cast<IdT>(probe_label(slots, mask, static_cast<long long>(seg_load<IdT>(in, i))));
 }
 
-// lookup of the sequence with device-side counts: two id arrays of the same
-// (device) length, relabelled into two outputs (in place is fine); a == nullptr
-// skips the first array
+// lookup of the sequence with device-side counts, when it does not ride on another launch
 template <typename IdT>
-__global__ void __launch_bounds__(RL_BLOCK)
-relabel_lookup_pair_kernel(const IdT* a, const IdT* b, const Count nc, const Count n_keys,
-                           const Slot* __restrict__ slots, IdT* out_a, IdT* out_b) {
+__global__ void __launch_bounds__(RL_BLOCK) relabel_lookup_pair_kernel(const LookupJob job) {
   pdl_enter();
-  const int64_t n = count_of(nc);
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
-  if (i >= n) return;
-  const uint64_t mask = slots_for(count_of(n_keys)) - 1;
-  if (a != nullptr) out_a[i] = static_cast<IdT>(probe_label(slots, mask, static_cast<long long>(a[i])));
-  out_b[i] = static_cast<IdT>(probe_label(slots, mask, static_cast<long long>(b[i])));
+  run_lookup_cta<IdT>(job, blockIdx.x);
 }
 
 inline int64_t seg_total(const dgs_segments& s) {
@@ -299,11 +243,11 @@ __global__ void zero_word_kernel(int64_t* w) { *w = 0; }
 
 // insert -> count -> number over a cleared table; n_bound sizes the grids
 template <typename IdT, typename Keys>
-int run_unique(const Keys& keys, Count n_keys, const TableView& t, void* unique_out, int64_t unique_capacity,
-               int64_t* n_unique, int32_t* status, cudaStream_t s) {
+int run_unique(const Keys& keys, Count n_keys, const TableSize& size, const TableView& t, void* unique_out,
+               int64_t unique_capacity, int64_t* n_unique, int32_t* status, cudaStream_t s) {
   const unsigned per_key_grid = static_cast<unsigned>((n_keys.bound + RL_BLOCK - 1) / RL_BLOCK);
-  DGS_CUDA_TRY(launch_chained(relabel_insert_kernel<IdT, Keys>, per_key_grid, RL_BLOCK, s, keys, t.slots, t.slot_of,
-                              status));
+  DGS_CUDA_TRY(launch_chained(relabel_insert_kernel<IdT, Keys>, per_key_grid, RL_BLOCK, s, keys, size, t.slots,
+                              t.slot_of, status));
   DGS_CUDA_TRY(launch_chained(relabel_count_kernel, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, n_keys, t.slots,
                               t.slot_of, t.tile_off, t.ticket, t.total, n_unique));
   DGS_CUDA_TRY(launch_chained(relabel_number_kernel<IdT, Keys>, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, keys,
@@ -316,36 +260,43 @@ int run_unique(const Keys& keys, Count n_keys, const TableView& t, void* unique_
 int64_t* unique_total(void* table, int64_t key_bound) { return table_view(table, key_bound).total; }
 unsigned int* unique_ticket(void* table, int64_t key_bound) { return table_view(table, key_bound).ticket; }
 
-int launch_unique_pair(bool ids64, const void* a, Count na, const void* b, Count nb, int64_t key_bound,
-                       void* table, void* unique_out, int64_t unique_capacity, int64_t* n_unique_out,
-                       int32_t* status, cudaStream_t s) {
-  DGS_REQUIRE(key_bound > 0 && key_bound < (1ll << 30) && na.bound + nb.bound <= key_bound, DGS_ERR_UNSUPPORTED,
-              "relabel: %lld keys", (long long)key_bound);
+ClearJob make_clear_job(void* table, int64_t key_bound, const TableSize& size) {
   const TableView t = table_view(table, key_bound);
-  const Count n_keys{key_bound, na.dev, nb.dev};
-  DGS_REQUIRE(na.dev != nullptr && nb.dev != nullptr && na.dev2 == nullptr && nb.dev2 == nullptr, DGS_ERR_INVALID,
-              "relabel: the pair form takes one device word per length");
-  const PairKeys keys{a, b, na, nb};
-  const uint64_t cap = slots_for(key_bound);
-  DGS_CUDA_TRY(launch_chained(relabel_clear_kernel, static_cast<unsigned>((cap + RL_BLOCK * 4 - 1) / (RL_BLOCK * 4)),
-                              RL_BLOCK, s, t.slots, n_keys));
-  return ids64 ? run_unique<int64_t, PairKeys>(keys, n_keys, t, unique_out, unique_capacity, n_unique_out, status, s)
-               : run_unique<int32_t, PairKeys>(keys, n_keys, t, unique_out, unique_capacity, n_unique_out, status, s);
+  return ClearJob{t.slots, size, static_cast<unsigned>((t.cap + CLEAR_SLOTS_PER_CTA - 1) / CLEAR_SLOTS_PER_CTA)};
 }
 
-int launch_lookup_pair(const void* table, int64_t key_bound, Count n_keys, bool ids64, const void* a,
-                       const void* b, Count n, void* out_a, void* out_b, cudaStream_t s) {
-  if (n.bound == 0) return DGS_OK;
+LookupJob make_lookup_job(const void* table, int64_t key_bound, const TableSize& size, const void* a, const void* b,
+                          Count n, void* out_a, void* out_b) {
   const TableView t = table_view(const_cast<void*>(table), key_bound);
-  const unsigned grid = static_cast<unsigned>((n.bound + RL_BLOCK - 1) / RL_BLOCK);
-  if (ids64)
-    DGS_CUDA_TRY(launch_chained(relabel_lookup_pair_kernel<int64_t>, grid, RL_BLOCK, s, static_cast<const int64_t*>(a),
-                                static_cast<const int64_t*>(b), n, n_keys, t.slots, static_cast<int64_t*>(out_a),
-                                static_cast<int64_t*>(out_b)));
-  else
-    DGS_CUDA_TRY(launch_chained(relabel_lookup_pair_kernel<int32_t>, grid, RL_BLOCK, s, static_cast<const int32_t*>(a),
-                                static_cast<const int32_t*>(b), n, n_keys, t.slots, static_cast<int32_t*>(out_a),
-                                static_cast<int32_t*>(out_b)));
+  return LookupJob{a, b, out_a, out_b, n, t.slots, size, static_cast<unsigned>((n.bound + RL_BLOCK - 1) / RL_BLOCK)};
+}
+
+int launch_clear(const ClearJob& job, cudaStream_t s) {
+  if (job.ctas == 0) return DGS_OK;
+  DGS_CUDA_TRY(launch_chained(relabel_clear_kernel, job.ctas, RL_BLOCK, s, job));
+  return DGS_OK;
+}
+
+int launch_unique_pair(bool ids64, const void* a, Count na, const void* b, Count nb, int64_t key_bound,
+                       const TableSize& size, void* table, void* unique_out, int64_t unique_capacity,
+                       int64_t* n_unique_out, int32_t* status, cudaStream_t s) {
+  DGS_REQUIRE(key_bound > 0 && key_bound < (1ll << 30) && na.bound + nb.bound <= key_bound, DGS_ERR_UNSUPPORTED,
+              "relabel: %lld keys", (long long)key_bound);
+  DGS_REQUIRE(na.dev != nullptr && nb.dev != nullptr && na.dev2 == nullptr && nb.dev2 == nullptr, DGS_ERR_INVALID,
+              "relabel: the pair form takes one device word per length");
+  const TableView t = table_view(table, key_bound);
+  const Count n_keys{key_bound, na.dev, nb.dev};
+  const PairKeys keys{a, b, na, nb};
+  return ids64 ? run_unique<int64_t, PairKeys>(keys, n_keys, size, t, unique_out, unique_capacity, n_unique_out,
+                                               status, s)
+               : run_unique<int32_t, PairKeys>(keys, n_keys, size, t, unique_out, unique_capacity, n_unique_out,
+                                               status, s);
+}
+
+int launch_lookup(const LookupJob& job, bool ids64, cudaStream_t s) {
+  if (job.ctas == 0) return DGS_OK;
+  if (ids64) DGS_CUDA_TRY(launch_chained(relabel_lookup_pair_kernel<int64_t>, job.ctas, RL_BLOCK, s, job));
+  else DGS_CUDA_TRY(launch_chained(relabel_lookup_pair_kernel<int32_t>, job.ctas, RL_BLOCK, s, job));
   return DGS_OK;
 }
 
@@ -386,8 +337,9 @@ extern "C" int dgs_unique_first_occurrence(const dgs_segments* keys, int32_t ids
   DGS_CUDA_TRY(cudaMemsetAsync(t.slots, 0xFF, t.cap * sizeof(Slot), s));
   DGS_CUDA_TRY(cudaMemsetAsync(t.ticket, 0, sizeof(unsigned int), s));
   const SegKeys sk{*keys, n};
-  return ids64 ? run_unique<int64_t, SegKeys>(sk, exact_count(n), t, unique_out, n, n_unique, status, s)
-               : run_unique<int32_t, SegKeys>(sk, exact_count(n), t, unique_out, n, n_unique, status, s);
+  const TableSize size{exact_count(n), 1};
+  return ids64 ? run_unique<int64_t, SegKeys>(sk, exact_count(n), size, t, unique_out, n, n_unique, status, s)
+               : run_unique<int32_t, SegKeys>(sk, exact_count(n), size, t, unique_out, n, n_unique, status, s);
 }
 
 extern "C" int dgs_relabel_lookup(const void* table, size_t table_bytes, int64_t n_keys_built,

@@ -1,0 +1,109 @@
+// Device-side pieces of the relabel table that more than one translation unit
+// needs: the slot layout, the hash, and the two jobs (clearing a table, looking
+// labels up) that the multi-hop sequence runs as extra CTAs of another kernel's
+// launch instead of as launches of their own.
+#pragma once
+#include "common.cuh"
+
+namespace dgs {
+
+constexpr int RL_BLOCK = 256;
+constexpr unsigned long long LABEL_BIT = 0x8000000000000000ull;
+constexpr long long EMPTY_KEY = -1;  // cleared slot: key = -1, value = 2^64-1
+constexpr uint32_t NO_SLOT = 0xFFFFFFFFu;
+constexpr int CLEAR_SLOTS_PER_CTA = RL_BLOCK * 4;
+
+struct __align__(16) Slot {
+  long long key;
+  unsigned long long val;
+};
+
+// slots in use for a table built for n keys: the power of two >= max(2n, 64)
+__host__ __device__ __forceinline__ uint64_t slots_for(int64_t n) {
+  uint64_t want = 2 * static_cast<uint64_t>(n);
+  if (want < 64) want = 64;
+#ifdef __CUDA_ARCH__
+  return 1ull << (64 - __clzll(static_cast<long long>(want - 1)));
+#else
+  uint64_t cap = 64;
+  while (cap < want) cap <<= 1;
+  return cap;
+#endif
+}
+
+// How many keys a table is dimensioned for: count_of(n) * mult.  The per-operator
+// path knows its key count (mult = 1).  The multi-hop sequence dimensions a hop's
+// table before that hop's neighbours are drawn, for seeds * (1 + fanout) keys.
+struct TableSize {
+  Count n;
+  int64_t mult;
+};
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint64_t table_slots(const TableSize& t) { return slots_for(count_of(t.n) * t.mult); }
+
+__device__ __forceinline__ uint64_t hash_key(long long key) {
+  uint64_t z = static_cast<uint64_t>(key);
+  z = (z ^ (z >> 33)) * 0xFF51AFD7ED558CCDull;
+  z = (z ^ (z >> 33)) * 0xC4CEB9FE1A85EC53ull;
+  return z ^ (z >> 33);
+}
+
+__device__ __forceinline__ long long probe_label(const Slot* __restrict__ slots, uint64_t mask, long long key) {
+  if (key < 0) return -1;
+  uint64_t h = hash_key(key) & mask;
+  for (uint64_t probes = 0; probes <= mask; ++probes) {
+    const Slot s = slots[h];  // one 16-byte load
+    if (s.key == key) return static_cast<long long>(s.val & ~LABEL_BIT);
+    if (s.key == EMPTY_KEY) break;
+    h = (h + 1) & mask;
+  }
+  return -1;
+}
+
+// ---- jobs that can ride on another kernel's launch -----------------------------
+// Clear the slots a table will use.  Runs before anything touches the table.
+struct ClearJob {
+  Slot* slots;
+  TableSize size;
+  unsigned ctas;  // CLEAR_SLOTS_PER_CTA slots each; 0: no job
+};
+__device__ __forceinline__ void run_clear_cta(const ClearJob& j, unsigned cta) {
+  const uint64_t cap = table_slots(j.size);
+  const uint64_t i = static_cast<uint64_t>(cta) * CLEAR_SLOTS_PER_CTA + threadIdx.x;
+  const ulonglong2 empty = make_ulonglong2(~0ull, ~0ull);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const uint64_t at = i + static_cast<uint64_t>(u) * RL_BLOCK;
+    if (at < cap) *reinterpret_cast<ulonglong2*>(&j.slots[at]) = empty;
+  }
+}
+
+// Relabel a finished hop's COO: out_a[i] = label(a[i]) (skipped when a is null),
+// out_b[i] = label(b[i]), i < n; in place is fine.  Needs that hop's numbering.
+struct LookupJob {
+  const void* a;
+  const void* b;
+  void* out_a;
+  void* out_b;
+  Count n;
+  const Slot* slots;
+  TableSize size;
+  unsigned ctas;  // RL_BLOCK ids each; 0: no job
+};
+template <typename IdT>
+__device__ __forceinline__ void run_lookup_cta(const LookupJob& j, unsigned cta) {
+  const int64_t n = count_of(j.n);
+  const int64_t i = static_cast<int64_t>(cta) * RL_BLOCK + threadIdx.x;
+  if (i >= n) return;
+  const uint64_t mask = table_slots(j.size) - 1;
+  if (j.a != nullptr)
+    static_cast<IdT*>(j.out_a)[i] =
+        static_cast<IdT>(probe_label(j.slots, mask, static_cast<long long>(static_cast<const IdT*>(j.a)[i])));
+  static_cast<IdT*>(j.out_b)[i] =
+      static_cast<IdT>(probe_label(j.slots, mask, static_cast<long long>(static_cast<const IdT*>(j.b)[i])));
+}
+
+#endif  // __CUDACC__
+}  // namespace dgs

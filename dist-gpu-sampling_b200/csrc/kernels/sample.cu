@@ -95,10 +95,17 @@ sample_plan_kernel(const __grid_constant__ dgs_chunk_desc indptr, const IdT* __r
                    const Count nc, const int64_t k, const bool replace,
                    int64_t* __restrict__ row_begin, int64_t* __restrict__ deg_out,
                    int64_t* __restrict__ local_off, int64_t* tile_sums, int64_t* total_out,
-                   unsigned int* ticket, int64_t* nnz_out, int32_t* __restrict__ status) {
+                   unsigned int* ticket, int64_t* nnz_out, const unsigned int plan_tiles,
+                   const ClearJob clear, const LookupJob lookup, int32_t* __restrict__ status) {
   __shared__ int64_t smem[SAMPLE_BLOCK / 32 + 1];
   constexpr int sh = sizeof(IdT) == 8 ? 3 : 2;
   pdl_enter();
+  if (blockIdx.x >= plan_tiles) {  // CTAs beyond the plan's tiles carry the independent jobs
+    const unsigned int extra = blockIdx.x - plan_tiles;
+    if (extra < clear.ctas) run_clear_cta(clear, extra);
+    else run_lookup_cta<IdT>(lookup, extra - clear.ctas);
+    return;
+  }
   const int64_t n = count_of(nc);
   const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + threadIdx.x;
   int64_t cnt = 0;
@@ -128,7 +135,7 @@ sample_plan_kernel(const __grid_constant__ dgs_chunk_desc indptr, const IdT* __r
   if (i < n) local_off[i] = ex;
 
   // publish the tile sum; the CTA that draws the last ticket scans all of them
-  publish_and_scan_tiles<SAMPLE_BLOCK>(total, tile_sums, ticket, total_out, nnz_out, smem);
+  publish_and_scan_tiles<SAMPLE_BLOCK>(total, tile_sums, ticket, total_out, nnz_out, smem, plan_tiles);
 }
 
 // ---------------------------------------------------------------------------
@@ -564,10 +571,12 @@ int check_sample_args(const char* who, const void* seeds, int64_t n, int64_t k, 
 
 template <typename IdT>
 int plan_typed(const dgs_chunk_desc& indptr, const void* seeds, Count n, int64_t k, bool replace,
-               const PlanView& pv, int64_t* nnz, int32_t* status, cudaStream_t s) {
-  DGS_CUDA_TRY(launch_chained(sample_plan_kernel<IdT>, static_cast<unsigned>(pv.ntiles), SAMPLE_BLOCK, s, indptr,
+               const PlanView& pv, int64_t* nnz, const ClearJob& clear, const LookupJob& lookup, int32_t* status,
+               cudaStream_t s) {
+  const unsigned tiles = static_cast<unsigned>(pv.ntiles);
+  DGS_CUDA_TRY(launch_chained(sample_plan_kernel<IdT>, tiles + clear.ctas + lookup.ctas, SAMPLE_BLOCK, s, indptr,
                               static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
-                              pv.tile_off, pv.total, pv.ticket, nnz, status));
+                              pv.tile_off, pv.total, pv.ticket, nnz, tiles, clear, lookup, status));
   return DGS_OK;
 }
 
@@ -612,12 +621,13 @@ uint64_t sample_rng_key(uint64_t rng_seed, uint64_t rng_offset) {
 }
 
 int launch_sample_plan(const dgs_chunk_desc& indptr, const void* seeds, bool ids64, Count n, int64_t k,
-                       bool replace, void* plan, int64_t* nnz_out, bool zero_ticket, int32_t* status,
-                       cudaStream_t s) {
+                       bool replace, void* plan, int64_t* nnz_out, bool zero_ticket, const ClearJob& clear,
+                       const LookupJob& lookup, int32_t* status, cudaStream_t s) {
+  static_assert(SAMPLE_BLOCK == RL_BLOCK, "the jobs riding on the plan launch assume its CTA size");
   const PlanView pv = plan_view(plan, n.bound);
   if (zero_ticket) DGS_CUDA_TRY(cudaMemsetAsync(pv.ticket, 0, sizeof(unsigned int), s));
-  return ids64 ? plan_typed<int64_t>(indptr, seeds, n, k, replace, pv, nnz_out, status, s)
-               : plan_typed<int32_t>(indptr, seeds, n, k, replace, pv, nnz_out, status, s);
+  return ids64 ? plan_typed<int64_t>(indptr, seeds, n, k, replace, pv, nnz_out, clear, lookup, status, s)
+               : plan_typed<int32_t>(indptr, seeds, n, k, replace, pv, nnz_out, clear, lookup, status, s);
 }
 
 int launch_sample_uniform(const dgs_chunk_desc& indices, const void* seeds, bool ids64, Count n, int64_t k,
@@ -668,7 +678,8 @@ extern "C" int dgs_sample_plan(const dgs_chunk_desc* indptr, const void* seeds, 
     }
     return DGS_OK;
   }
-  return launch_sample_plan(*indptr, seeds, ids64 != 0, exact_count(n), k, replace != 0, plan, nnz, true, status, s);
+  return launch_sample_plan(*indptr, seeds, ids64 != 0, exact_count(n), k, replace != 0, plan, nnz, true, ClearJob{},
+                            LookupJob{}, status, s);
 }
 
 extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* seeds, int32_t ids64,

@@ -50,20 +50,24 @@ tile_scan_kernel(int64_t* __restrict__ sums, const int64_t ntiles, int64_t* __re
 // atomic counter that must be zero at launch; nobody waits on anybody) scans
 // all tile sums in place and publishes the total.  `smem` needs BLOCK/32 + 1
 // entries; must be called by all threads of the CTA.
+// The tiles are CTAs 0 .. ntiles-1 of the launch (the launch may hold further CTAs
+// with other work, which do not call this).
 template <int BLOCK>
 __device__ __forceinline__ void publish_and_scan_tiles(int64_t my_tile_sum, int64_t* tile_sums,
                                                        unsigned int* ticket, int64_t* total_dev,
-                                                       int64_t* total_out, int64_t* smem) {
+                                                       int64_t* total_out, int64_t* smem,
+                                                       unsigned int n_tiles = 0) {
   __shared__ bool s_last;
+  if (n_tiles == 0) n_tiles = gridDim.x;
   if (threadIdx.x == 0) {
     tile_sums[blockIdx.x] = my_tile_sum;
     __threadfence();
-    s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    s_last = atomicAdd(ticket, 1u) == n_tiles - 1;
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  const int64_t ntiles = gridDim.x;
+  const int64_t ntiles = n_tiles;
   int64_t carry = 0;
   for (int64_t t0 = 0; t0 < ntiles; t0 += BLOCK) {
     const int64_t t = t0 + threadIdx.x;
