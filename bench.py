@@ -71,6 +71,8 @@ def workload(args):
 LAUNCHES_SAMPLE = 2   # plan (+ tile scan in its last CTA), sample
 LAUNCHES_RELABEL = 4  # insert, count (+ tile scan in its last CTA), number, lookup
 LAUNCHES_GATHER = 1
+API_NAMES = {True: "_CAPI_sample_blocks* (all hops queued as one sequence, one size read-back per step)",
+             False: "reference operator sequence: _CAPI_sample_neighbors* + _CAPI_tensor_relabel per hop"}
 LAUNCHES_HOP_FUSED = 5  # plan (+ table clear + previous hop's lookup), sample, insert, count, number
 LAUNCHES_STEP_FUSED = 2  # init words, last hop's lookup
 # DRAM bytes per gathered row (read + write) from the ncu capture summarised in
@@ -92,9 +94,10 @@ def parse_args():
                     help="sample with per-edge fp32 U(0,1) weights (the weighted operator) instead of uniformly")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--fused", action="store_true",
-                    help="run each step's hops through _CAPI_sample_blocks* (one queued sequence, one size "
-                         "read-back) instead of one sampling and one relabel operator per hop")
+    ap.add_argument("--api", default="blocks", choices=["blocks", "per-hop"],
+                    help="blocks: each step's hops go through _CAPI_sample_blocks* (one queued sequence, one size "
+                         "read-back); per-hop: the reference's operator sequence, one sampling and one relabel "
+                         "operator per hop.  The other one is timed too and reported beside the headline.")
     return ap.parse_args()
 
 
@@ -191,7 +194,8 @@ def config_dict(args, w, n_edges_graph, world):
                                                    nodes, n_edges_graph, w["gamma"], nodes, dim),
             "fanouts": w["fanouts"], "batch_per_rank": args.batch, "global_batch": args.batch * world,
             "train_set": w["train"], "replace": False, "weighted": bool(args.weighted),
-            "step": "%d x (%s + tensor_relabel) + features._CAPI_index(input_nodes)" % (len(w["fanouts"]), op),
+            "step": "sample_blocks over %d hops = %d x (%s + tensor_relabel), then features._CAPI_index(input_nodes)"
+                    % (len(w["fanouts"]), len(w["fanouts"]), op),
             "storage": "indptr/indices/features in ChunkTensors split evenly over %d GPU(s), %s" % (world, tail),
             "l2": "inputs larger than L2 (indices %.2f GB, features %.2f GB); a new seed batch every step"
                   % (n_edges_graph * 8 / 1e9, nodes * dim * 4 / 1e9)}
@@ -331,9 +335,12 @@ def main_ours(args):
     dev_batches = host_batches.to(dev)
     torch.manual_seed(1234 + rank)
 
-    def step(seeds):
+    has_blocks = hasattr(torch.ops.dgs_ops, "_CAPI_sample_blocks")     # absent from the reference's own library
+    main_fused = args.api == "blocks" and has_blocks
+
+    def step(seeds, fused=None):
         frontier, blocks, n_edges = pkg.sample_blocks(seeds, fanouts, c_indptr, c_indices, probs=c_probs,
-                                                      fused=args.fused)
+                                                      fused=main_fused if fused is None else fused)
         return frontier, n_edges
 
     def barrier():
@@ -394,6 +401,24 @@ def main_ours(args):
     e2e_ms = e0.elapsed_time(e1)
     clock_info = clocks.stop(n_before, n_after) if rank == 0 else None
 
+    # ---- the same K steps through the other API, for the record ----
+    other_ms, other_edges = 0.0, 0
+    if has_blocks:
+        for s in range(min(args.warmup, 5)):
+            fr, _ = step(dev_batches[my[s % len(my)]], fused=not main_fused)
+            c_feats._CAPI_index(fr)
+        barrier()
+        o0 = torch.cuda.Event(enable_timing=True)
+        o1 = torch.cuda.Event(enable_timing=True)
+        o0.record()
+        for s in range(args.steps):
+            fr, e = step(dev_batches[my[(args.warmup + s) % len(my)]], fused=not main_fused)
+            x = c_feats._CAPI_index(fr)
+            other_edges += e
+        o1.record()
+        barrier()
+        other_ms = o0.elapsed_time(o1)
+
     # ---- the gather kernel on its own: back-to-back launches over the last frontiers, so that the events
     # bracket the kernel and not the host's launch gap (inside a step the host is still busy returning
     # from the relabel operator when the GPU reaches the gather) ----
@@ -413,13 +438,13 @@ def main_ours(args):
     del kept
 
     # ---- reduce over ranks: max time, summed work ----
-    stats = torch.tensor([total_ms, sample_ms, gather_ms, e2e_ms], dtype=torch.float64, device=dev)
-    work = torch.tensor([edges, rows, e2e_edges], dtype=torch.float64, device=dev)
+    stats = torch.tensor([total_ms, sample_ms, gather_ms, e2e_ms, other_ms], dtype=torch.float64, device=dev)
+    work = torch.tensor([edges, rows, e2e_edges, other_edges], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         dist.all_reduce(work, op=dist.ReduceOp.SUM)
-    total_ms, sample_ms, gather_ms, e2e_ms = stats.tolist()
-    edges_all, rows_all, e2e_edges_all = work.tolist()
+    total_ms, sample_ms, gather_ms, e2e_ms, other_ms = stats.tolist()
+    edges_all, rows_all, e2e_edges_all, other_edges_all = work.tolist()
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
@@ -443,10 +468,11 @@ def main_ours(args):
                           "gather_payload_gbs_all_ranks": rows_all * dim * 4 / (gather_ms * 1e-3) / 1e9},
             "e2e": {"value": e2e_edges_all / (e2e_ms * 1e-3), "unit": "edges/s",
                     "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * ((LAUNCHES_STEP_FUSED + len(fanouts) * LAUNCHES_HOP_FUSED if args.fused else
+            "gpu_launches": args.steps * ((LAUNCHES_STEP_FUSED + len(fanouts) * LAUNCHES_HOP_FUSED if main_fused else
                                            len(fanouts) * (LAUNCHES_SAMPLE + LAUNCHES_RELABEL)) + LAUNCHES_GATHER),
-            "api": "_CAPI_sample_blocks* (all hops queued as one sequence)" if args.fused
-                   else "reference operator sequence: _CAPI_sample_neighbors* + _CAPI_tensor_relabel per hop",
+            "api": API_NAMES[main_fused],
+            "other_api": {"api": API_NAMES[not main_fused], "value": other_edges_all / (other_ms * 1e-3),
+                          "unit": "edges/s", "ms_per_step": other_ms / args.steps} if other_ms > 0 else None,
             "roofline": {"kernel": "gather_rows_kernel (features._CAPI_index)", "bound": "hbm",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind,
