@@ -19,13 +19,16 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-// DGS_NO_PDL=1 launches every kernel the plain way (no programmatic stream serialization)
-bool chained_launches_enabled() {
-  static const bool on = [] {
+// DGS_NO_PDL=1 launches every kernel the plain way (no programmatic stream serialization);
+// DGS_PDL_OFF_MASK=<hex> does so for the launch sites whose bit is set
+bool chained_launches_enabled(int site) {
+  static const unsigned long off = [] {
     const char* e = std::getenv("DGS_NO_PDL");
-    return !(e != nullptr && e[0] == '1');
+    if (e != nullptr && e[0] == '1') return ~0ul;
+    const char* m = std::getenv("DGS_PDL_OFF_MASK");
+    return m != nullptr ? std::strtoul(m, nullptr, 16) : 0ul;
   }();
-  return on;
+  return ((off >> site) & 1ul) == 0;
 }
 
 int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {

@@ -155,7 +155,7 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
     init.tickets[init.n_tickets++] = sample_plan_ticket(plan[h], hops[h].seed_bound);
     init.tickets[init.n_tickets++] = unique_ticket(table[h], key_bound);
   }
-  DGS_CUDA_TRY(launch_chained(blocks_init_kernel, 1u, 32u, s, init));
+  DGS_CUDA_TRY(launch_chained(SITE_INIT, blocks_init_kernel, 1u, 32u, s, init));
 
   // ---- queue every hop; no size is read back in between ----
   const void* hop_seeds = seeds;

@@ -72,10 +72,13 @@ __device__ __forceinline__ void pdl_enter() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-bool chained_launches_enabled();  // false with DGS_NO_PDL=1 (host/error.cc)
+// which launch this is; DGS_NO_PDL=1 turns the attribute off everywhere, DGS_PDL_OFF_MASK=<hex> per site
+enum LaunchSite { SITE_INIT = 0, SITE_PLAN, SITE_SAMPLE, SITE_INSERT, SITE_COUNT, SITE_NUMBER, SITE_LOOKUP,
+                  SITE_GATHER, SITE_CLEAR };
+bool chained_launches_enabled(int site);  // host/error.cc
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_chained(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t s,
+inline cudaError_t launch_chained(int site, void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t s,
                                   Args&&... args) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid, 1, 1);
@@ -86,7 +89,7 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), unsigned grid, unsig
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = chained_launches_enabled() ? 1 : 0;
+  cfg.numAttrs = chained_launches_enabled(site) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -256,7 +256,7 @@ int launch_gather(const Src& rows, int64_t n, int64_t D, int sh, void* out, cons
       nvec == 1 ? 0u : static_cast<uint32_t>(((1ull << 32) + nvec - 1) / nvec);
   const int64_t tiles = (n + rows_per_tile - 1) / rows_per_tile;
   DGS_REQUIRE(tiles <= 0x7fffffffLL, DGS_ERR_UNSUPPORTED, "gather: too many rows (%lld)", (long long)n);
-  DGS_CUDA_TRY(launch_chained(gather_rows_kernel<Src, VEC>, static_cast<unsigned>(tiles), GATHER_BLOCK, stream, rows,
+  DGS_CUDA_TRY(launch_chained(SITE_GATHER, gather_rows_kernel<Src, VEC>, static_cast<unsigned>(tiles), GATHER_BLOCK, stream, rows,
                               n, D, sh, nvec, rows_per_tile, magic, slot_shift, static_cast<char*>(out), order, status));
   return DGS_OK;
 }

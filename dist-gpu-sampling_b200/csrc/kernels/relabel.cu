@@ -246,11 +246,11 @@ template <typename IdT, typename Keys>
 int run_unique(const Keys& keys, Count n_keys, const TableSize& size, const TableView& t, void* unique_out,
                int64_t unique_capacity, int64_t* n_unique, int32_t* status, cudaStream_t s) {
   const unsigned per_key_grid = static_cast<unsigned>((n_keys.bound + RL_BLOCK - 1) / RL_BLOCK);
-  DGS_CUDA_TRY(launch_chained(relabel_insert_kernel<IdT, Keys>, per_key_grid, RL_BLOCK, s, keys, size, t.slots,
+  DGS_CUDA_TRY(launch_chained(SITE_INSERT, relabel_insert_kernel<IdT, Keys>, per_key_grid, RL_BLOCK, s, keys, size, t.slots,
                               t.slot_of, status));
-  DGS_CUDA_TRY(launch_chained(relabel_count_kernel, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, n_keys, t.slots,
+  DGS_CUDA_TRY(launch_chained(SITE_COUNT, relabel_count_kernel, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, n_keys, t.slots,
                               t.slot_of, t.tile_off, t.ticket, t.total, n_unique));
-  DGS_CUDA_TRY(launch_chained(relabel_number_kernel<IdT, Keys>, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, keys,
+  DGS_CUDA_TRY(launch_chained(SITE_NUMBER, relabel_number_kernel<IdT, Keys>, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, keys,
                               t.slots, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out), unique_capacity, status));
   return DGS_OK;
 }
@@ -273,7 +273,7 @@ LookupJob make_lookup_job(const void* table, int64_t key_bound, const TableSize&
 
 int launch_clear(const ClearJob& job, cudaStream_t s) {
   if (job.ctas == 0) return DGS_OK;
-  DGS_CUDA_TRY(launch_chained(relabel_clear_kernel, job.ctas, RL_BLOCK, s, job));
+  DGS_CUDA_TRY(launch_chained(SITE_CLEAR, relabel_clear_kernel, job.ctas, RL_BLOCK, s, job));
   return DGS_OK;
 }
 
@@ -295,8 +295,8 @@ int launch_unique_pair(bool ids64, const void* a, Count na, const void* b, Count
 
 int launch_lookup(const LookupJob& job, bool ids64, cudaStream_t s) {
   if (job.ctas == 0) return DGS_OK;
-  if (ids64) DGS_CUDA_TRY(launch_chained(relabel_lookup_pair_kernel<int64_t>, job.ctas, RL_BLOCK, s, job));
-  else DGS_CUDA_TRY(launch_chained(relabel_lookup_pair_kernel<int32_t>, job.ctas, RL_BLOCK, s, job));
+  if (ids64) DGS_CUDA_TRY(launch_chained(SITE_LOOKUP, relabel_lookup_pair_kernel<int64_t>, job.ctas, RL_BLOCK, s, job));
+  else DGS_CUDA_TRY(launch_chained(SITE_LOOKUP, relabel_lookup_pair_kernel<int32_t>, job.ctas, RL_BLOCK, s, job));
   return DGS_OK;
 }
 
@@ -358,10 +358,10 @@ extern "C" int dgs_relabel_lookup(const void* table, size_t table_bytes, int64_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>((n + RL_BLOCK - 1) / RL_BLOCK);
   if (ids64)
-    DGS_CUDA_TRY(launch_chained(relabel_lookup_kernel<int64_t>, grid, RL_BLOCK, s, *in, n, t.slots, t.cap - 1,
+    DGS_CUDA_TRY(launch_chained(SITE_LOOKUP, relabel_lookup_kernel<int64_t>, grid, RL_BLOCK, s, *in, n, t.slots, t.cap - 1,
                                 static_cast<int64_t*>(out)));
   else
-    DGS_CUDA_TRY(launch_chained(relabel_lookup_kernel<int32_t>, grid, RL_BLOCK, s, *in, n, t.slots, t.cap - 1,
+    DGS_CUDA_TRY(launch_chained(SITE_LOOKUP, relabel_lookup_kernel<int32_t>, grid, RL_BLOCK, s, *in, n, t.slots, t.cap - 1,
                                 static_cast<int32_t*>(out)));
   return DGS_OK;
 }

@@ -574,7 +574,7 @@ int plan_typed(const dgs_chunk_desc& indptr, const void* seeds, Count n, int64_t
                const PlanView& pv, int64_t* nnz, const ClearJob& clear, const LookupJob& lookup, int32_t* status,
                cudaStream_t s) {
   const unsigned tiles = static_cast<unsigned>(pv.ntiles);
-  DGS_CUDA_TRY(launch_chained(sample_plan_kernel<IdT>, tiles + clear.ctas + lookup.ctas, SAMPLE_BLOCK, s, indptr,
+  DGS_CUDA_TRY(launch_chained(SITE_PLAN, sample_plan_kernel<IdT>, tiles + clear.ctas + lookup.ctas, SAMPLE_BLOCK, s, indptr,
                               static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
                               pv.tile_off, pv.total, pv.ticket, nnz, tiles, clear, lookup, status));
   return DGS_OK;
@@ -585,7 +585,7 @@ int uniform_typed(const dgs_chunk_desc& indices, const void* seeds, Count n, int
                   const PlanView& pv, const uint32_t* order, uint64_t key, void* coo_row, void* coo_col,
                   int64_t cap, int64_t* pos, bool rowpos, int32_t* status, cudaStream_t s) {
 #define DGS_LAUNCH_U(G)                                                                                      \
-  DGS_CUDA_TRY(launch_chained(sample_uniform_kernel<IdT, G>,                                                 \
+  DGS_CUDA_TRY(launch_chained(SITE_SAMPLE, sample_uniform_kernel<IdT, G>,                                                 \
                               static_cast<unsigned>((n.bound + SAMPLE_BLOCK / G - 1) / (SAMPLE_BLOCK / G)),  \
                               SAMPLE_BLOCK, s, indices, static_cast<const IdT*>(seeds), n, k, replace,       \
                               pv.row_begin, pv.deg, pv.local_off, pv.tile_off, order, key,                   \
@@ -604,7 +604,7 @@ int weighted_typed(const dgs_chunk_desc& indices, const dgs_chunk_desc& probs, c
                    void* coo_row, void* coo_col, int64_t cap, int64_t* pos, bool rowpos, int32_t* status,
                    cudaStream_t s) {
   const unsigned grid = static_cast<unsigned>((n.bound + SAMPLE_BLOCK / 32 - 1) / (SAMPLE_BLOCK / 32));
-  DGS_CUDA_TRY(launch_chained(sample_weighted_kernel<IdT>, grid, SAMPLE_BLOCK, s, indices, probs,
+  DGS_CUDA_TRY(launch_chained(SITE_SAMPLE, sample_weighted_kernel<IdT>, grid, SAMPLE_BLOCK, s, indices, probs,
                               static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
                               pv.tile_off, order, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap,
                               pos, rowpos, status));
