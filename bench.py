@@ -2,11 +2,17 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                   [--workload products|papers100m|friendster|small] [--batch 1024] [--weighted] [--scale F]
+                  [--api blocks|per-hop]
 
-One step = one mini-batch per rank through the reference-facing operators:
-  for fan_out in reversed([15, 10, 5]):  sample_neighbors_with_chunk_tensor -> tensor_relabel
-  x = features._CAPI_index(input_nodes)
-on a Products-shaped synthetic graph (2,449,029 nodes, ~123.7 M edges, Chung-Lu
+One step = one mini-batch per rank:
+  frontier, blocks = sample_blocks(seeds, [15, 10, 5])      # sample + relabel, fan-outs applied last to first
+  x = features._CAPI_index(frontier)
+The hop loop runs through `_CAPI_sample_blocks_with_chunk_tensor` (all hops queued as one
+launch sequence, one size read-back per step; `--api blocks`, the default) or through the
+reference's own operator sequence, `_CAPI_sample_neighbors_with_chunk_tensor` +
+`_CAPI_tensor_relabel` per hop (`--api per-hop`).  Whichever is not the headline is timed
+over the same K steps in the same run and reported as `other_api`.  The graph is
+a Products-shaped synthetic graph (2,449,029 nodes, ~123.7 M edges, Chung-Lu
 power law, 100 fp32 features per node) whose indptr / indices / features live in
 ChunkTensors split evenly over the N GPUs of the node (weak scaling: every rank
 samples its own 1,024-seed batches).  `--workload papers100m` is the
