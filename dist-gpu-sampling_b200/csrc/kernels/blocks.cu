@@ -161,6 +161,8 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
   const void* hop_seeds = seeds;
   const int64_t* n_dev = n0_dev;
   LookupJob pending{};  // relabelling of the previous hop's COO, carried by the next plan launch
+  SizesReport report{};
+  report.dst = sizes;
   for (int h = 0; h < n_hops; ++h) {
     const dgs_hop& hp = hops[h];
     const int64_t k = hp.fanout;
@@ -169,7 +171,7 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
     const Count n{hp.seed_bound, n_dev, nullptr};
     // the table is dimensioned before the neighbours are drawn: seeds * (1 + fanout) keys at most
     const TableSize size{n, 1 + k};
-    rc = launch_sample_plan(*indptr, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], &sizes[2 * h], false,
+    rc = launch_sample_plan(*indptr, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], nullptr, false,
                             make_clear_job(table[h], key_bound, size), pending, status, s);
     if (rc != DGS_OK) return rc;
     const int64_t* nnz_dev = sample_plan_total(plan[h], hp.seed_bound);
@@ -182,8 +184,11 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
                                      hp.coo_row, hp.coo_col, edge_bound, nullptr, row_is_position, status, s);
     if (rc != DGS_OK) return rc;
     const Count nnz{edge_bound, nnz_dev, nullptr};
+    report.src[2 * h] = nnz_dev;
+    report.src[2 * h + 1] = unique_total(table[h], key_bound);
+    if (h == n_hops - 1) report.n = 2 * n_hops;  // the last hop's count kernel sends all sizes to the host at once
     rc = launch_unique_pair(ids64 != 0, hop_seeds, n, hp.coo_col, nnz, key_bound, size, table[h], hp.frontier,
-                            hp.frontier_bound, &sizes[2 * h + 1], status, s);
+                            hp.frontier_bound, nullptr, report, status, s);
     if (rc != DGS_OK) return rc;
     pending = make_lookup_job(table[h], key_bound, size, row_is_position ? nullptr : hp.coo_row, hp.coo_col, nnz,
                               hp.coo_row, hp.coo_col);

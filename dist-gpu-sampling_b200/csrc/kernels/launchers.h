@@ -45,10 +45,11 @@ int launch_lookup(const LookupJob& job, bool ids64, cudaStream_t s);
 // First-occurrence unique of the logical concatenation a[0:na) ++ b[0:nb) whose
 // lengths are device words, into a table that has been cleared.  unique_out holds
 // unique_capacity ids; a larger result raises DGS_ERR_RANGE in the status word and
-// is cut off.  The table's ticket word must be zero at launch (it resets itself).
+// is cut off.  The table's ticket word must be zero at launch (it resets itself).  `report`
+// (n may be 0) is carried out by the kernel that knows the number of distinct keys.
 int launch_unique_pair(bool ids64, const void* a, Count na, const void* b, Count nb, int64_t key_bound,
                        const TableSize& size, void* table, void* unique_out, int64_t unique_capacity,
-                       int64_t* n_unique_out, int32_t* status, cudaStream_t s);
+                       int64_t* n_unique_out, const SizesReport& report, int32_t* status, cudaStream_t s);
 int64_t* unique_total(void* table, int64_t key_bound);
 unsigned int* unique_ticket(void* table, int64_t key_bound);
 

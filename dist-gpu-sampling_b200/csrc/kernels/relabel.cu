@@ -140,7 +140,7 @@ relabel_insert_kernel(const __grid_constant__ Keys keys, const TableSize size, S
 __global__ void __launch_bounds__(RL_BLOCK)
 relabel_count_kernel(const Count nc, const Slot* __restrict__ slots,
                      const uint32_t* __restrict__ slot_of, int64_t* tile_sums, unsigned int* ticket,
-                     int64_t* total_dev, int64_t* n_unique_out) {
+                     int64_t* total_dev, int64_t* n_unique_out, const SizesReport report) {
   __shared__ int s_cnt;
   __shared__ int64_t s_scan[RL_BLOCK / 32 + 1];
   pdl_enter();
@@ -161,8 +161,12 @@ relabel_count_kernel(const Count nc, const Slot* __restrict__ slots,
   for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(FULL_MASK, c, o);
   if ((threadIdx.x & 31) == 0 && c) atomicAdd(&s_cnt, c);
   __syncthreads();
-  publish_and_scan_tiles<RL_BLOCK>(static_cast<int64_t>(s_cnt), tile_sums, ticket, total_dev, n_unique_out,
-                                   s_scan);
+  const bool last = publish_and_scan_tiles<RL_BLOCK>(static_cast<int64_t>(s_cnt), tile_sums, ticket, total_dev,
+                                                     n_unique_out, s_scan);
+  if (last && threadIdx.x == 0 && report.n > 0) {  // same thread that wrote *total_dev just above
+    for (int k = 0; k < report.n; ++k) report.dst[k] = *report.src[k];
+    __threadfence_system();
+  }
 }
 
 // pass 3: number the first occurrences, emit them, store the label in the slot
@@ -244,12 +248,13 @@ __global__ void zero_word_kernel(int64_t* w) { *w = 0; }
 // insert -> count -> number over a cleared table; n_bound sizes the grids
 template <typename IdT, typename Keys>
 int run_unique(const Keys& keys, Count n_keys, const TableSize& size, const TableView& t, void* unique_out,
-               int64_t unique_capacity, int64_t* n_unique, int32_t* status, cudaStream_t s) {
+               int64_t unique_capacity, int64_t* n_unique, const SizesReport& report, int32_t* status,
+               cudaStream_t s) {
   const unsigned per_key_grid = static_cast<unsigned>((n_keys.bound + RL_BLOCK - 1) / RL_BLOCK);
   DGS_CUDA_TRY(launch_chained(SITE_INSERT, relabel_insert_kernel<IdT, Keys>, per_key_grid, RL_BLOCK, s, keys, size, t.slots,
                               t.slot_of, status));
   DGS_CUDA_TRY(launch_chained(SITE_COUNT, relabel_count_kernel, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, n_keys, t.slots,
-                              t.slot_of, t.tile_off, t.ticket, t.total, n_unique));
+                              t.slot_of, t.tile_off, t.ticket, t.total, n_unique, report));
   DGS_CUDA_TRY(launch_chained(SITE_NUMBER, relabel_number_kernel<IdT, Keys>, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, keys,
                               t.slots, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out), unique_capacity, status));
   return DGS_OK;
@@ -279,7 +284,7 @@ int launch_clear(const ClearJob& job, cudaStream_t s) {
 
 int launch_unique_pair(bool ids64, const void* a, Count na, const void* b, Count nb, int64_t key_bound,
                        const TableSize& size, void* table, void* unique_out, int64_t unique_capacity,
-                       int64_t* n_unique_out, int32_t* status, cudaStream_t s) {
+                       int64_t* n_unique_out, const SizesReport& report, int32_t* status, cudaStream_t s) {
   DGS_REQUIRE(key_bound > 0 && key_bound < (1ll << 30) && na.bound + nb.bound <= key_bound, DGS_ERR_UNSUPPORTED,
               "relabel: %lld keys", (long long)key_bound);
   DGS_REQUIRE(na.dev != nullptr && nb.dev != nullptr && na.dev2 == nullptr && nb.dev2 == nullptr, DGS_ERR_INVALID,
@@ -288,9 +293,9 @@ int launch_unique_pair(bool ids64, const void* a, Count na, const void* b, Count
   const Count n_keys{key_bound, na.dev, nb.dev};
   const PairKeys keys{a, b, na, nb};
   return ids64 ? run_unique<int64_t, PairKeys>(keys, n_keys, size, t, unique_out, unique_capacity, n_unique_out,
-                                               status, s)
+                                               report, status, s)
                : run_unique<int32_t, PairKeys>(keys, n_keys, size, t, unique_out, unique_capacity, n_unique_out,
-                                               status, s);
+                                               report, status, s);
 }
 
 int launch_lookup(const LookupJob& job, bool ids64, cudaStream_t s) {
@@ -338,8 +343,10 @@ extern "C" int dgs_unique_first_occurrence(const dgs_segments* keys, int32_t ids
   DGS_CUDA_TRY(cudaMemsetAsync(t.ticket, 0, sizeof(unsigned int), s));
   const SegKeys sk{*keys, n};
   const TableSize size{exact_count(n), 1};
-  return ids64 ? run_unique<int64_t, SegKeys>(sk, exact_count(n), size, t, unique_out, n, n_unique, status, s)
-               : run_unique<int32_t, SegKeys>(sk, exact_count(n), size, t, unique_out, n, n_unique, status, s);
+  return ids64 ? run_unique<int64_t, SegKeys>(sk, exact_count(n), size, t, unique_out, n, n_unique, SizesReport{},
+                                              status, s)
+               : run_unique<int32_t, SegKeys>(sk, exact_count(n), size, t, unique_out, n, n_unique, SizesReport{},
+                                              status, s);
 }
 
 extern "C" int dgs_relabel_lookup(const void* table, size_t table_bytes, int64_t n_keys_built,

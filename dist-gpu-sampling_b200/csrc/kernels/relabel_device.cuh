@@ -39,6 +39,15 @@ struct TableSize {
   int64_t mult;
 };
 
+// Sizes that only the host needs (how much of each output is valid): device words copied to a
+// host-visible array by the kernel that computes the last of them, so that a sequence of kernels
+// pays for one write over the host link instead of one per size.
+struct SizesReport {
+  int64_t* dst;  // [n], pinned
+  int n;         // 0: nothing to report
+  const int64_t* src[2 * DGS_MAX_HOPS];
+};
+
 #ifdef __CUDACC__
 
 __device__ __forceinline__ uint64_t table_slots(const TableSize& t) { return slots_for(count_of(t.n) * t.mult); }

@@ -49,11 +49,11 @@ tile_scan_kernel(int64_t* __restrict__ sums, const int64_t ntiles, int64_t* __re
 // this after computing its tile sum.  The CTA that draws the last ticket (an
 // atomic counter that must be zero at launch; nobody waits on anybody) scans
 // all tile sums in place and publishes the total.  `smem` needs BLOCK/32 + 1
-// entries; must be called by all threads of the CTA.
+// entries; must be called by all threads of the CTA.  Returns true in that last CTA.
 // The tiles are CTAs 0 .. ntiles-1 of the launch (the launch may hold further CTAs
 // with other work, which do not call this).
 template <int BLOCK>
-__device__ __forceinline__ void publish_and_scan_tiles(int64_t my_tile_sum, int64_t* tile_sums,
+__device__ __forceinline__ bool publish_and_scan_tiles(int64_t my_tile_sum, int64_t* tile_sums,
                                                        unsigned int* ticket, int64_t* total_dev,
                                                        int64_t* total_out, int64_t* smem,
                                                        unsigned int n_tiles = 0) {
@@ -65,7 +65,7 @@ __device__ __forceinline__ void publish_and_scan_tiles(int64_t my_tile_sum, int6
     s_last = atomicAdd(ticket, 1u) == n_tiles - 1;
   }
   __syncthreads();
-  if (!s_last) return;
+  if (!s_last) return false;
   __threadfence();
   const int64_t ntiles = n_tiles;
   int64_t carry = 0;
@@ -85,6 +85,7 @@ __device__ __forceinline__ void publish_and_scan_tiles(int64_t my_tile_sum, int6
       __threadfence_system();
     }
   }
+  return true;  // this CTA was the last one: the totals are final
 }
 
 }  // namespace dgs
