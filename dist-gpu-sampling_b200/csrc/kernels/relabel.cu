@@ -67,6 +67,7 @@ struct SegKeys {
   dgs_segments s;
   int64_t n;
   __device__ __forceinline__ int64_t size() const { return n; }
+  __device__ __forceinline__ int64_t bound() const { return n; }
   template <typename IdT>
   __device__ __forceinline__ IdT load(int64_t i) const {
     return seg_load<IdT>(s, i);
@@ -79,6 +80,7 @@ struct PairKeys {
   const void* b;
   Count na, nb;
   __device__ __forceinline__ int64_t size() const { return count_of(na) + count_of(nb); }
+  __device__ __forceinline__ int64_t bound() const { return na.bound + nb.bound; }
   template <typename IdT>
   __device__ __forceinline__ IdT load(int64_t i) const {
     const int64_t x = count_of(na);
@@ -146,16 +148,17 @@ relabel_count_kernel(const Count nc, const Slot* __restrict__ slots,
   pdl_enter();
   if (threadIdx.x == 0) s_cnt = 0;
   __syncthreads();
-  const int64_t n = count_of(nc);
   const int64_t base = static_cast<int64_t>(blockIdx.x) * RL_TILE + threadIdx.x * RL_ITEMS;
+  // slot_of has room for nc.bound entries: read it while the live count is still on its way
+  uint32_t sl[RL_ITEMS];
+#pragma unroll
+  for (int u = 0; u < RL_ITEMS; ++u) sl[u] = base + u < nc.bound ? slot_of[base + u] : NO_SLOT;
+  const int64_t n = count_of(nc);
   int c = 0;
 #pragma unroll
   for (int u = 0; u < RL_ITEMS; ++u) {
     const int64_t i = base + u;
-    if (i < n) {
-      const uint32_t s = slot_of[i];
-      if (s != NO_SLOT && slots[s].val == static_cast<unsigned long long>(i)) ++c;
-    }
+    if (i < n && sl[u] != NO_SLOT && slots[sl[u]].val == static_cast<unsigned long long>(i)) ++c;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(FULL_MASK, c, o);
@@ -177,18 +180,20 @@ relabel_number_kernel(const __grid_constant__ Keys keys, Slot* slots, const uint
                       const int64_t unique_capacity, int32_t* __restrict__ status) {
   __shared__ int smem[RL_BLOCK / 32 + 1];
   pdl_enter();
-  const int64_t n = keys.size();
   const int64_t base = static_cast<int64_t>(blockIdx.x) * RL_TILE + threadIdx.x * RL_ITEMS;
   bool first[RL_ITEMS];
   uint32_t slot[RL_ITEMS];
+  const int64_t room = keys.bound();
+#pragma unroll
+  for (int u = 0; u < RL_ITEMS; ++u) slot[u] = base + u < room ? slot_of[base + u] : NO_SLOT;  // ahead of the count
+  const int64_t n = keys.size();
   int c = 0;
 #pragma unroll
   for (int u = 0; u < RL_ITEMS; ++u) {
     const int64_t i = base + u;
     first[u] = false;
-    slot[u] = NO_SLOT;
+    if (i >= n) slot[u] = NO_SLOT;
     if (i < n) {
-      slot[u] = slot_of[i];
       // a slot already relabelled by another CTA carries LABEL_BIT and cannot equal i
       first[u] = slot[u] != NO_SLOT &&
                  *reinterpret_cast<const volatile unsigned long long*>(&slots[slot[u]].val) ==

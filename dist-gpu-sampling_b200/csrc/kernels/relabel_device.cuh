@@ -103,15 +103,15 @@ struct LookupJob {
 };
 template <typename IdT>
 __device__ __forceinline__ void run_lookup_cta(const LookupJob& j, unsigned cta) {
-  const int64_t n = count_of(j.n);
   const int64_t i = static_cast<int64_t>(cta) * RL_BLOCK + threadIdx.x;
-  if (i >= n) return;
+  // the ids are read while the live count and the table size are still on their way (room for n.bound ids)
+  const bool in_bound = i < j.n.bound;
+  const long long ka = (in_bound && j.a != nullptr) ? static_cast<long long>(static_cast<const IdT*>(j.a)[i]) : -1;
+  const long long kb = in_bound ? static_cast<long long>(static_cast<const IdT*>(j.b)[i]) : -1;
+  if (i >= count_of(j.n)) return;
   const uint64_t mask = table_slots(j.size) - 1;
-  if (j.a != nullptr)
-    static_cast<IdT*>(j.out_a)[i] =
-        static_cast<IdT>(probe_label(j.slots, mask, static_cast<long long>(static_cast<const IdT*>(j.a)[i])));
-  static_cast<IdT*>(j.out_b)[i] =
-      static_cast<IdT>(probe_label(j.slots, mask, static_cast<long long>(static_cast<const IdT*>(j.b)[i])));
+  if (j.a != nullptr) static_cast<IdT*>(j.out_a)[i] = static_cast<IdT>(probe_label(j.slots, mask, ka));
+  static_cast<IdT*>(j.out_b)[i] = static_cast<IdT>(probe_label(j.slots, mask, kb));
 }
 
 #endif  // __CUDACC__

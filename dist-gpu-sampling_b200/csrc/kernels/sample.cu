@@ -106,11 +106,14 @@ sample_plan_kernel(const __grid_constant__ dgs_chunk_desc indptr, const IdT* __r
     else run_lookup_cta<IdT>(lookup, extra - clear.ctas);
     return;
   }
-  const int64_t n = count_of(nc);
   const int64_t i = static_cast<int64_t>(blockIdx.x) * SAMPLE_TILE + threadIdx.x;
+  // the seed is read before the live count arrives (the list has room for nc.bound entries), so that
+  // the two round trips overlap; an entry past the count is never used
+  const IdT seed_raw = i < nc.bound ? seeds[i] : IdT(0);
+  const int64_t n = count_of(nc);
   int64_t cnt = 0;
   if (i < n) {
-    const int64_t s = static_cast<int64_t>(seeds[i]);
+    const int64_t s = static_cast<int64_t>(seed_raw);
     int64_t rb = 0, deg = 0;
     if (s < 0 || s + 1 >= indptr.total) {
       raise_status(status, DGS_ERR_RANGE);
@@ -200,7 +203,6 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
                       const bool row_is_position, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
   pdl_enter();
-  const int64_t n = count_of(nc);
   constexpr int GROUPS = SAMPLE_BLOCK / G;  // seeds per CTA
   constexpr int TAKEN_WORDS = 4096;         // 16 KB of position bitmaps per CTA, split between its groups
   __shared__ uint32_t s_taken[TAKEN_WORDS];
@@ -213,12 +215,16 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
 
   {  // one seed per group; all 32 lanes of a warp walk through the same code
     const int64_t slot = static_cast<int64_t>(blockIdx.x) * GROUPS + group;
-    const bool valid = slot < n;
+    // everything that only needs the slot is read before the live count arrives (all arrays have room for
+    // nc.bound entries); what belongs to a slot past the count is dropped below
+    const bool in_bound = slot < nc.bound;
     // which seed this group serves: the slot itself, or the slot's entry of the processing order
-    const int64_t i = (valid && order != nullptr) ? static_cast<int64_t>(order[slot]) : slot;
-    const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, valid);
-    const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
-    const int64_t seed = !valid ? 0 : (row_is_position ? i : static_cast<int64_t>(seeds[i]));
+    const int64_t i = (in_bound && order != nullptr) ? static_cast<int64_t>(order[slot]) : slot;
+    const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, in_bound);
+    const int64_t seed_raw = !in_bound ? 0 : (row_is_position ? i : static_cast<int64_t>(seeds[i]));
+    const bool valid = slot < count_of(nc);
+    const int64_t deg = valid ? sp.deg : 0, rb = valid ? sp.rb : 0, o = valid ? sp.o : 0;
+    const int64_t seed = valid ? seed_raw : 0;
     const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
 
     if (replace) {
