@@ -121,3 +121,23 @@ def test_sample_blocks_bounds_and_workspace(abi, pkg):
     assert abi.dgs_sample_blocks_bounds(1 << 28, applied, 1, 1 << 40, hops) != 0
     assert b"keys" in abi.dgs_last_error()
     assert abi.dgs_sample_blocks_workspace_bytes(None, 3) == 0
+
+
+def test_added_operators_have_the_documented_schemas(pkg):
+    """The one-sequence hop loop: four operators beside the reference's (no counterpart in src/pybind.cc)."""
+    import torch
+    pkg.load_ops()
+    ct = "__torch__.torch.classes.dgs_classes.ChunkTensor"
+    ret = " -> (Tensor _0, Tensor[] _1, Tensor[] _2, int[] _3)"
+    expect = {
+        "_CAPI_sample_blocks": "(Tensor _0, Tensor _1, Tensor _2, int[] _3, bool _4)" + ret,
+        "_CAPI_sample_blocks_with_chunk_tensor": "(Tensor _0, %s _1, %s _2, int[] _3, bool _4)" % (ct, ct) + ret,
+        "_CAPI_sample_blocks_with_probs": "(Tensor _0, Tensor _1, Tensor _2, Tensor _3, int[] _4, bool _5)" + ret,
+        "_CAPI_sample_blocks_with_probs_with_chunk_tensor":
+            "(Tensor _0, %s _1, %s _2, %s _3, int[] _4, bool _5)" % (ct, ct, ct) + ret,
+    }
+    for name, sig in expect.items():
+        assert str(torch._C._get_schema("dgs_ops::" + name, "")) == "dgs_ops::" + name + sig
+    cpu = torch.arange(4)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        torch.ops.dgs_ops._CAPI_sample_blocks(cpu, cpu, cpu, [2, 2], False)
