@@ -173,14 +173,25 @@ def create_dgs_communicator(group_size, local_group=None):
     torch.ops.dgs_ops._CAPI_set_nccl(group_size, broadcast_list[0], dist.get_rank() % group_size)
 
 
-def cached_size_per_gpu(total_bytes, num_gpus, available_mem, cache_rate=1.0):
-    """Capacity rule of create_chunktensor (chunktensor_sampler.py:39-43)."""
-    return int(min(total_bytes * cache_rate // num_gpus, available_mem))
+def cached_size_per_gpu(total_bytes, num_gpus, available_mem, cache_rate=1.0, row_bytes=None):
+    """Capacity rule of create_chunktensor (chunktensor_sampler.py:39-43): an equal share of the cached part,
+    limited by the memory that is free.  With row_bytes the result is rounded down to whole rows, so that no
+    row straddles two chunks and every row keeps the alignment of the first (the reference's rule cuts chunks
+    at arbitrary bytes; the gather then has to fall back to narrower loads for the chunks after the first)."""
+    cap = int(min(total_bytes * cache_rate // num_gpus, available_mem))
+    if row_bytes:
+        # a whole number of rows, and of 16-byte vectors when the row size allows it
+        unit = row_bytes
+        while unit % 16 and unit < 16 * row_bytes:
+            unit += row_bytes
+        cap = max(cap // unit * unit, min(cap, unit) // row_bytes * row_bytes)
+    return cap
 
 
 def create_chunktensor(tensor, num_gpus, available_mem, cache_rate=1.0, root_rank=0, local_group=None):
     """chunktensor_sampler.py:32-60: the root rank decides the capacity, every rank
-    constructs the ChunkTensor (collective), the root loads the data."""
+    constructs the ChunkTensor (collective), the root loads the data.  Capacities are whole rows
+    (see cached_size_per_gpu)."""
     import torch
     import torch.distributed as dist
     load_ops()
@@ -188,7 +199,9 @@ def create_chunktensor(tensor, num_gpus, available_mem, cache_rate=1.0, root_ran
     rank = dist.get_rank() if distributed else 0
     if rank == root_rank:
         total = tensor.numel() * tensor.element_size()
-        meta = [list(tensor.shape), tensor.dtype, cached_size_per_gpu(total, num_gpus, available_mem, cache_rate)]
+        row_bytes = tensor.element_size() * (tensor.shape[1] if tensor.dim() == 2 else 1)
+        meta = [list(tensor.shape), tensor.dtype,
+                cached_size_per_gpu(total, num_gpus, available_mem, cache_rate, row_bytes)]
     else:
         meta = [None, None, None]
     if distributed:

@@ -141,3 +141,16 @@ def test_added_operators_have_the_documented_schemas(pkg):
     cpu = torch.arange(4)
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         torch.ops.dgs_ops._CAPI_sample_blocks(cpu, cpu, cpu, [2, 2], False)
+
+
+def test_capacity_rule_keeps_whole_rows(pkg):
+    """cached_size_per_gpu: the reference's rule (chunktensor_sampler.py:39-43), optionally cut to whole rows."""
+    f = pkg.cached_size_per_gpu
+    total = 2_449_029 * 400
+    assert f(total, 8, 10 ** 12) == total // 8                       # the reference's value: mid-row, 8-byte aligned only
+    cap = f(total, 8, 10 ** 12, 1.0, 400)
+    assert cap <= total // 8 and cap % 400 == 0 and cap % 16 == 0 and total // 8 - cap < 2000
+    assert f(total, 8, 10 ** 6, 1.0, 400) == 10 ** 6 // 2000 * 2000  # limited by the free memory, still whole rows
+    assert f(1000, 3, 10 ** 9, 1.0, 8) == 320 and f(60, 2, 10 ** 9, 1.0, 12) == 24
+    assert f(100, 3, 10 ** 9, 1.0, 400) == 0                          # not even one row: everything in the host tail
+    assert f(total, 8, 10 ** 12, 0.5, 400) <= total // 16
