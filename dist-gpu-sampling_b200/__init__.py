@@ -188,10 +188,11 @@ def cached_size_per_gpu(total_bytes, num_gpus, available_mem, cache_rate=1.0, ro
     return cap
 
 
-def create_chunktensor(tensor, num_gpus, available_mem, cache_rate=1.0, root_rank=0, local_group=None):
+def create_chunktensor(tensor, num_gpus, available_mem, cache_rate=1.0, root_rank=0, local_group=None,
+                       whole_rows=True):
     """chunktensor_sampler.py:32-60: the root rank decides the capacity, every rank
     constructs the ChunkTensor (collective), the root loads the data.  Capacities are whole rows
-    (see cached_size_per_gpu)."""
+    (see cached_size_per_gpu); whole_rows=False gives the reference's byte-exact rule."""
     import torch
     import torch.distributed as dist
     load_ops()
@@ -201,7 +202,7 @@ def create_chunktensor(tensor, num_gpus, available_mem, cache_rate=1.0, root_ran
         total = tensor.numel() * tensor.element_size()
         row_bytes = tensor.element_size() * (tensor.shape[1] if tensor.dim() == 2 else 1)
         meta = [list(tensor.shape), tensor.dtype,
-                cached_size_per_gpu(total, num_gpus, available_mem, cache_rate, row_bytes)]
+                cached_size_per_gpu(total, num_gpus, available_mem, cache_rate, row_bytes if whole_rows else None)]
     else:
         meta = [None, None, None]
     if distributed:

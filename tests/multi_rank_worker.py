@@ -39,7 +39,7 @@ def main():
     rows, D = 6000, 100
     table = rng.standard_normal((rows, D)).astype(np.float32)
     cap = 4 * (D * (rows // (world + 1)) + 36)            # not row aligned; ~1/(world+1) of the rows on the host
-    ct = pkg.create_chunktensor(torch.from_numpy(table), world, cap, cache_rate=1.0)
+    ct = pkg.create_chunktensor(torch.from_numpy(table), world, cap, cache_rate=1.0, whole_rows=False)
     cm = o.ChunkModel([rows, D], np.float32, min(cap, table.nbytes // world), world=world)
     cm.load(table)
     assert cm.host_n > 0
