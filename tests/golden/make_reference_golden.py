@@ -5,13 +5,12 @@ deterministic outputs can only be recorded on a GPU box.  This script loads the
 library built by oracle/build_reference.sh (oracle/_ref/libdgs_reference.so --
 the reference's unmodified kernels compiled for sm_100a), runs every operator on
 small seeded inputs whose result does not depend on random numbers, and writes
-
-    gpurun_out/reference_b200.json      (copy it to tests/golden/)
+the file given as its argument (default: reference_b200.json beside this script).
 
 It must run in a process of its own: the reference and this repository register
 the same torch class and operator names.
 
-    python tests/golden/make_reference_golden.py
+    python tests/golden/make_reference_golden.py [output.json]
 
 What is recorded: placement views (the README demo and a 2-D table with a host
 tail), _CAPI_index / split_index / local / host index, tensor_relabel (int64 and
@@ -148,8 +147,8 @@ def main():
                     "fetched_bits": fetched.cpu().numpy().view(np.int32).tolist()}
     torch.cuda.synchronize()
     del c_ip, c_ix, c_pr
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    path = os.path.join(ROOT, "gpurun_out", "reference_b200.json")
+    path = sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "reference_b200.json")
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
     with open(path, "w") as f:
         json.dump(out, f)
     print("wrote", path, os.path.getsize(path), "bytes")
