@@ -7,7 +7,7 @@ rank -> device part 0..24, host part 25..99).
 
 oracle_small.json is produced by the pinned CPU oracle (oracle/dgs_oracle.c) on
 seeded inputs; it freezes the oracle's deterministic outputs (placement, index,
-split-index, relabel, full-row sampling) so that a later change of the oracle
+split-index, relabel, full-row sampling, the multi-hop loop) so that a later change of the oracle
 cannot silently move the target the CUDA path is compared against.
 
 Run from the repository root:  python tests/golden/make_golden.py
@@ -67,6 +67,17 @@ def main():
     row, col = o.sample_uniform(indptr, indices, seeds, 5, False)
     cases["full_rows"] = {"indptr": indptr.tolist(), "indices": indices.tolist(), "seeds": seeds.tolist(),
                           "k": 5, "coo_row": row.tolist(), "coo_col": col.tolist()}
+    # the multi-hop loop (sample -> relabel per fan-out, last fan-out first) where nothing is random:
+    # every degree is below every fan-out
+    deg = rng.integers(0, 5, size=300)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, 300, size=int(indptr[-1])).astype(np.int64)
+    seeds = rng.permutation(300)[:24].astype(np.int64)
+    frontier, blocks, n_edges = o.sample_blocks(indptr, indices, seeds, [6, 5, 7])
+    cases["blocks"] = {"indptr": indptr.tolist(), "indices": indices.tolist(), "seeds": seeds.tolist(),
+                       "fanouts": [6, 5, 7], "frontier": frontier.tolist(), "n_edges": int(n_edges),
+                       "blocks": [{"coo_row": r.tolist(), "coo_col": c.tolist(), "n_src": int(ns), "n_dst": int(nd)}
+                                  for r, c, ns, nd in blocks]}
     with open(os.path.join(HERE, "oracle_small.json"), "w") as f:
         json.dump(cases, f)
     print("wrote golden fixtures")

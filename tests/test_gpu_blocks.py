@@ -87,6 +87,23 @@ def test_blocks_without_random_choice_equal_the_oracle(ops, oracle, pkg, idt):
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and a[2:] == b[2:]
 
 
+@pytest.mark.parametrize("idt", [torch.int64, torch.int32])
+@pytest.mark.parametrize("fused", [True, False])
+def test_blocks_match_the_frozen_fixture(ops, pkg, idt, fused):
+    """tests/golden/oracle_small.json "blocks": the loop's one possible answer when no row is longer than a
+    fan-out, through the one-sequence operators and through the per-hop operators."""
+    import json
+    import os
+    g = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_small.json")))["blocks"]
+    f, blocks, n_edges = pkg.sample_blocks(to_dev(np.array(g["seeds"]), idt), g["fanouts"],
+                                           to_dev(np.array(g["indptr"]), idt), to_dev(np.array(g["indices"]), idt),
+                                           fused=fused)
+    assert n_edges == g["n_edges"] and f.dtype == idt and f.tolist() == g["frontier"]
+    assert len(blocks) == len(g["blocks"])
+    for (r, c, ns, nd), e in zip(blocks, g["blocks"]):
+        assert r.tolist() == e["coo_row"] and c.tolist() == e["coo_col"] and (ns, nd) == (e["n_src"], e["n_dst"])
+
+
 @pytest.mark.parametrize("fanouts,replace", [([15, 10, 5], False), ([10, 10], False), ([3, 4], True), ([40, 2], False)])
 def test_blocks_uniform_valid(ops, oracle, pkg, fanouts, replace):
     rng = np.random.default_rng(11)

@@ -172,3 +172,14 @@ def test_cache_fetch_oracle(oracle):
     pos = {int(k): i for i, k in enumerate(keys)}
     exp = np.stack([gpu[pos[int(x)]] if int(x) in pos else cpu[int(x)] for x in nid])
     assert out.tobytes() == exp.tobytes()
+
+
+def test_oracle_reproduces_the_frozen_multi_hop_loop(oracle):
+    """The sample -> relabel loop over fan-outs [6, 5, 7] on a graph whose degrees are all below 5:
+    nothing is random, so frontier and blocks are one fixed answer."""
+    g = json.load(open(os.path.join(GOLDEN, "oracle_small.json")))["blocks"]
+    f, blocks, n_edges = oracle.sample_blocks(np.array(g["indptr"]), np.array(g["indices"]), np.array(g["seeds"]),
+                                              g["fanouts"])
+    assert n_edges == g["n_edges"] and f.tolist() == g["frontier"]
+    for (r, c, ns, nd), e in zip(blocks, g["blocks"]):
+        assert r.tolist() == e["coo_row"] and c.tolist() == e["coo_col"] and (ns, nd) == (e["n_src"], e["n_dst"])
