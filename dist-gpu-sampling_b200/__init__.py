@@ -255,3 +255,23 @@ def sample_blocks(seeds, fanouts, indptr, indices, probs=None, replace=False, fu
         blocks.insert(0, (coo_row, coo_col, frontier.numel(), seeds.numel()))
         seeds = frontier
     return seeds, blocks, n_edges
+
+
+def block_csc(coo_row, coo_col, n_dst, rows_sorted=True):
+    """CSC form of one sampled block, for a GNN layer that wants (indptr, indices) instead of COO.
+
+    coo_row holds relabelled destination ids (positions of the seeds), coo_col relabelled source ids.
+    The samplers emit edges grouped by seed position, so with a duplicate-free seed list coo_row is already
+    non-decreasing and the column order is the CSC order (rows_sorted=True: no sort).  With repeated seeds
+    (rows_sorted=False) the edges are first brought into destination order by a stable sort.
+    Returns (indptr[n_dst + 1], indices) on coo_row's device; the DGL-free counterpart of the
+    dgl.create_block call in chunktensor_sampler.py:112-116.
+    """
+    import torch
+    if not rows_sorted:
+        order = torch.sort(coo_row, stable=True).indices
+        coo_row, coo_col = coo_row[order], coo_col[order]
+    indptr = torch.zeros(n_dst + 1, dtype=torch.int64, device=coo_row.device)
+    if coo_row.numel():
+        indptr[1:] = torch.cumsum(torch.bincount(coo_row.to(torch.int64), minlength=n_dst)[:n_dst], 0)
+    return indptr, coo_col

@@ -154,3 +154,24 @@ def test_capacity_rule_keeps_whole_rows(pkg):
     assert f(1000, 3, 10 ** 9, 1.0, 8) == 320 and f(60, 2, 10 ** 9, 1.0, 12) == 24
     assert f(100, 3, 10 ** 9, 1.0, 400) == 0                          # not even one row: everything in the host tail
     assert f(total, 8, 10 ** 12, 0.5, 400) <= total // 16
+
+
+def test_block_csc_from_the_frozen_blocks(pkg):
+    """block_csc turns a sampled block's COO into (indptr, indices); checked on the frozen multi-hop fixture."""
+    import json
+    import torch
+    g = json.load(open(os.path.join(ROOT, "tests", "golden", "oracle_small.json")))["blocks"]
+    for b in g["blocks"]:
+        row, col = torch.tensor(b["coo_row"]), torch.tensor(b["coo_col"])
+        indptr, indices = pkg.block_csc(row, col, b["n_dst"])
+        assert indptr.numel() == b["n_dst"] + 1 and indptr[0] == 0 and indptr[-1] == row.numel()
+        for d in range(b["n_dst"]):
+            assert indices[indptr[d]:indptr[d + 1]].tolist() == col[row == d].tolist()
+        # a shuffled COO needs the sort and then gives the same neighbour sets
+        perm = torch.randperm(row.numel(), generator=torch.Generator().manual_seed(1))
+        ip2, ix2 = pkg.block_csc(row[perm], col[perm], b["n_dst"], rows_sorted=False)
+        assert ip2.tolist() == indptr.tolist()
+        for d in range(b["n_dst"]):
+            assert sorted(ix2[ip2[d]:ip2[d + 1]].tolist()) == sorted(col[row == d].tolist())
+    empty = torch.empty(0, dtype=torch.int64)
+    assert pkg.block_csc(empty, empty, 3)[0].tolist() == [0, 0, 0, 0]
