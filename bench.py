@@ -83,7 +83,7 @@ LAUNCHES_HOP_FUSED = 5  # plan (+ table clear + previous hop's lookup), sample, 
 LAUNCHES_STEP_FUSED = 2  # init words, last hop's lookup
 # DRAM bytes per gathered row (read + write) from the ncu capture summarised in
 # profiles/; None until a capture exists for the benchmarked row width
-NCU_TRAFFIC_BYTES_PER_ROW = {100: 860.7}
+NCU_TRAFFIC_BYTES_PER_ROW = {100: 861.2}
 
 
 def parse_args():
