@@ -175,3 +175,51 @@ def test_block_csc_from_the_frozen_blocks(pkg):
             assert sorted(ix2[ip2[d]:ip2[d + 1]].tolist()) == sorted(col[row == d].tolist())
     empty = torch.empty(0, dtype=torch.int64)
     assert pkg.block_csc(empty, empty, 3)[0].tolist() == [0, 0, 0, 0]
+
+
+def test_sample_blocks_rejects_bad_arguments_before_any_launch(abi, pkg):
+    """Argument errors of dgs_sample_blocks are return codes with a message; none of these reaches CUDA."""
+    def desc(total, esz=8):
+        d = pkg.ChunkDesc()
+        d.total = d.threshold = d.each = total
+        d.num_parts, d.esz = 1, esz
+        d.dev[0] = 0x1000                    # never dereferenced on the host
+        return d
+    ip, ix = desc(101), desc(500)
+    hops = (pkg.Hop * 2)()
+    assert abi.dgs_sample_blocks_bounds(10, (ctypes.c_int64 * 2)(3, 2), 2, 100, hops) == 0
+    for h in hops:
+        h.coo_row = h.coo_col = h.frontier = 0x2000
+    sizes = (ctypes.c_int64 * 4)()
+    args = dict(indptr=ctypes.byref(ip), indices=ctypes.byref(ix), probs=None, seeds=0x3000, ids64=1, hops=hops,
+                n_hops=2, replace=0, ws=0x4000, ws_bytes=abi.dgs_sample_blocks_workspace_bytes(hops, 2),
+                sizes=ctypes.cast(sizes, ctypes.c_void_p))
+
+    def call(**kw):
+        a = dict(args, **kw)
+        return abi.dgs_sample_blocks(a["indptr"], a["indices"], a["probs"], a["seeds"], a["ids64"], a["hops"],
+                                     a["n_hops"], a["replace"], 1, 0, a["ws"], a["ws_bytes"], a["sizes"], None, None)
+
+    INVALID, UNSUPPORTED = 1, 5
+    assert call(indptr=None) == INVALID and b"null descriptor" in abi.dgs_last_error()
+    assert call(n_hops=0) == INVALID and call(n_hops=9) == INVALID
+    assert call(ids64=0) == INVALID and b"element size" in abi.dgs_last_error()      # int64 graph, int32 ids
+    assert call(sizes=None) == INVALID
+    assert call(seeds=None) == INVALID
+    assert call(ws_bytes=16) == INVALID and b"workspace" in abi.dgs_last_error()
+    assert call(ws=0x4008) == INVALID                                                # not 16-byte aligned
+    bad = (pkg.Hop * 2)()
+    ctypes.memmove(bad, hops, ctypes.sizeof(bad))
+    bad[1].seed_bound += 1                                                           # chain of bounds broken
+    assert call(hops=bad) == INVALID and b"previous hop" in abi.dgs_last_error()
+    ctypes.memmove(bad, hops, ctypes.sizeof(bad))
+    bad[0].coo_col = None
+    assert call(hops=bad) == INVALID and b"null output" in abi.dgs_last_error()
+    pr = desc(500, esz=8)
+    assert call(probs=ctypes.byref(pr)) == UNSUPPORTED and b"fp32" in abi.dgs_last_error()
+    pr = desc(500, esz=4)
+    big = (pkg.Hop * 1)()
+    assert abi.dgs_sample_blocks_bounds(10, (ctypes.c_int64 * 1)(40), 1, 100, big) == 0
+    big[0].coo_row = big[0].coo_col = big[0].frontier = 0x2000
+    assert call(probs=ctypes.byref(pr), hops=big, n_hops=1,
+                ws_bytes=abi.dgs_sample_blocks_workspace_bytes(big, 1)) == UNSUPPORTED      # weighted fan-out > 32
