@@ -11,7 +11,12 @@ with a bandwidth measured on the machine it runs on.
 
   python dist-gpu-sampling_b200/index_microbench.py --rows 4000000 --dim 128 --ids 1000000
   python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
-      dist-gpu-sampling_b200/index_microbench.py --rows 8000000 --host-frac 0.2
+      dist-gpu-sampling_b200/index_microbench.py --rows 8000000 --host-frac 0.2 \
+      --ids 1000,16000,256000,1000000,4000000 --dist zipf
+
+--ids takes a list (one query size after the other on the same table), --dist uniform|zipf picks the id
+distribution (Zipf(1.1) ranks mapped to rows by a fixed permutation), --misalign B adds B bytes to the
+capacity so that chunk boundaries fall inside rows (the straddle and off-grid paths of the gather).
 
 The table is filled in place, chunk by chunk, with a hash of the flat element
 index, so every gathered row can be verified without a second copy.
