@@ -40,22 +40,16 @@ def build(force=False, verbose=False):
 def load_ops():
     """torch.ops.load_library on libdgs.so -- the call a user of the reference
     makes with its libdgs.so (example/dgs_create_communicator.py:4)."""
+    path = binding_path()
     if not _loaded["ops"]:
         import torch
-        # DGS_OPS_LIBRARY points the same calls at another build of the operator library -- e.g. the
-        # reference's own kernels compiled for this GPU (oracle/build_reference.sh) for a side-by-side run
-        path = os.environ.get("DGS_OPS_LIBRARY") or binding_path()
         if not os.path.exists(path):
             raise RuntimeError(
                 "dgs-b200: %s is missing; run `python __graft_entry__.py` (or build.py) first. "
                 "There is no fallback path." % path)
         torch.ops.load_library(path)
         _loaded["ops"] = True
-        if os.environ.get("DGS_OPS_LIBRARY") and not (torch.distributed.is_available()
-                                                      and torch.distributed.is_initialized()):
-            # the reference's ChunkTensor constructor reads the communicator's size: give it a group of one
-            torch.ops.dgs_ops._CAPI_set_nccl(1, torch.ops.dgs_ops._CAPI_get_unique_id(), 0)
-    return os.environ.get("DGS_OPS_LIBRARY") or binding_path()
+    return path
 
 
 # ---------------------------------------------------------------------------
@@ -106,17 +100,16 @@ ABI_SIGNATURES = {
     "dgs_store_host_view": (ctypes.c_int, [_VP, ctypes.POINTER(_VP), _I64P]),
     "dgs_store_local_view": (ctypes.c_int, [_VP, ctypes.POINTER(_VP), _I64P]),
     "dgs_alloc_current_bytes": (_I64, []),
-    "dgs_locality_order_scratch_bytes": (_SZ, []),
-    "dgs_locality_order": (ctypes.c_int, [_VP, _I32, _I64, _I64, _VP, _VP, _SZ, _VP]),
-    "dgs_gather_rows": (ctypes.c_int, [_DP, _I32, _VP, _I32, _I64, _I64, _VP, _VP, _VP, _VP]),
+    "dgs_gather_rows": (ctypes.c_int, [_DP, _I32, _VP, _I32, _I64, _I64, _VP, _VP, _VP]),
+    "dgs_gather_rows_counted": (ctypes.c_int, [_DP, _VP, _I32, _I64, _VP, _I64, _VP, _VP, _VP]),
     "dgs_split_index_scratch_bytes": (_SZ, [_I64]),
     "dgs_split_index": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _VP, _VP, _VP, _SZ, _VP]),
     "dgs_split_index_static": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _VP, _VP, _VP]),
     "dgs_sample_plan_bytes": (_SZ, [_I64]),
     "dgs_sample_plan": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _I32, _VP, _VP, _VP, _VP]),
-    "dgs_sample_uniform": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _I32, _VP, _VP, _U64, _U64, _VP, _VP,
+    "dgs_sample_uniform": (ctypes.c_int, [_DP, _VP, _I32, _I64, _I64, _I32, _VP, _U64, _U64, _VP, _VP,
                                           _I64, _VP, _VP, _VP, _VP]),
-    "dgs_sample_weighted": (ctypes.c_int, [_DP, _DP, _VP, _I32, _I64, _I64, _I32, _VP, _VP, _U64, _U64, _VP,
+    "dgs_sample_weighted": (ctypes.c_int, [_DP, _DP, _VP, _I32, _I64, _I64, _I32, _VP, _U64, _U64, _VP,
                                            _VP, _I64, _VP, _VP, _VP, _VP]),
     "dgs_relabel_table_bytes": (_SZ, [_I64]),
     "dgs_unique_first_occurrence": (ctypes.c_int, [_SP, _I32, _VP, _SZ, _VP, _VP, _VP, _VP]),
@@ -125,6 +118,7 @@ ABI_SIGNATURES = {
     "dgs_sample_blocks_workspace_bytes": (_SZ, [_HP, _I32]),
     "dgs_sample_blocks": (ctypes.c_int, [_DP, _DP, _DP, _VP, _I32, _HP, _I32, _I32, _U64, _U64, _VP, _SZ, _VP, _VP,
                                          _VP]),
+    "dgs_sample_blocks_frontier_count": (_VP, [_HP, _I32, _VP]),
     "dgs_cache_table_slots": (_I64, [_I64]),
     "dgs_cache_build": (ctypes.c_int, [_VP, _VP, _I32, _I64, _VP, _VP, _I64, _VP, _VP]),
     "dgs_cache_fetch": (ctypes.c_int, [_VP, _I64, _DP, _VP, _I32, _I64, _I64, _VP, _VP, _I64, _VP, _VP, _VP]),
@@ -255,6 +249,51 @@ def sample_blocks(seeds, fanouts, indptr, indices, probs=None, replace=False, fu
         blocks.insert(0, (coo_row, coo_col, frontier.numel(), seeds.numel()))
         seeds = frontier
     return seeds, blocks, n_edges
+
+
+class PipelinedSampler:
+    """Mini-batches in flight: the role DGL's DataLoader plays around ChunkTensorSampler in the reference
+    (oppo_bench/single_node/chunktensor.py:120-172), on torch.classes.dgs_classes.BlockPipeline.
+
+        sampler = PipelinedSampler(indptr_ct, indices_ct, [15, 10, 5], features=feat_ct, max_seeds=1024, depth=3)
+        for input_nodes, blocks, n_edges, x in sampler(seed_batches):
+            ...   # blocks = [(coo_row, coo_col, n_src, n_dst)] in layer order, x = features[input_nodes]
+
+    `depth` batches are sampled (and their features gathered) ahead of the one being consumed, each on a
+    stream of its own, so the small hops of one batch overlap with the gather of another.  What a batch
+    yields are views into its slot: valid until `depth` - 1 further batches have been drawn from the
+    iterator; clone what must live longer.  indptr / indices / probs / features are ChunkTensors; seed
+    batches are tensors on the GPU or in (pinned) host memory, at most max_seeds ids each.  Results follow
+    the same rules as sample_blocks(): identical wherever no random choice is involved.
+    Delete the sampler before the ChunkTensors it reads (their destructor is collective).
+    """
+
+    def __init__(self, indptr, indices, fanouts, features=None, probs=None, replace=False, max_seeds=1024, depth=3):
+        import torch
+        load_ops()
+        self.depth = int(depth)
+        self.pipe = torch.classes.dgs_classes.BlockPipeline(indptr, indices, probs, features, list(fanouts),
+                                                            bool(replace), int(max_seeds), self.depth)
+
+    def submit(self, seeds):
+        self.pipe.submit(seeds)
+
+    def next(self):
+        frontier, rows, cols, shape, x = self.pipe.next()
+        blocks = [(rows[i], cols[i], shape[2 * i], shape[2 * i + 1]) for i in range(len(rows))]
+        return frontier, blocks, sum(r.numel() for r in rows), x
+
+    def __call__(self, seed_batches):
+        ahead = 0
+        for seeds in seed_batches:
+            self.pipe.submit(seeds)
+            ahead += 1
+            if ahead == self.depth:
+                yield self.next()
+                ahead -= 1
+        while ahead:
+            yield self.next()
+            ahead -= 1
 
 
 def block_csc(coo_row, coo_col, n_dst, rows_sorted=True):

@@ -25,7 +25,6 @@ ABI_SOURCES = [
     "kernels/sample.cu",
     "kernels/relabel.cu",
     "kernels/blocks.cu",
-    "kernels/order.cu",
     "host/error.cc",
     "host/comm.cc",
     "host/store.cc",
@@ -111,10 +110,11 @@ def build_binding(force=False, verbose=False):
     from torch.utils import cpp_extension
 
     src = os.path.join(CSRC, "binding", "ops.cc")
-    hdr = os.path.join(ROOT, "include", "dgs_b200.h")
+    hdrs = [os.path.join(ROOT, "include", "dgs_b200.h")] + \
+        [os.path.join(CSRC, "binding", h) for h in ("chunk_tensor.h", "host_words.h", "pipeline.h")]
     out = binding_path()
     stamp = out + ".sha"
-    dig = _digest([src, hdr], torch.__version__)
+    dig = _digest([src] + hdrs, torch.__version__)
     if not force and os.path.exists(out) and os.path.exists(stamp) and open(stamp).read() == dig:
         return ""
     tlib = os.path.join(os.path.dirname(torch.__file__), "lib")

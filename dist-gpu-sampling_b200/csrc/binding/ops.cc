@@ -1,8 +1,10 @@
 // PyTorch operator layer: torch.classes.dgs_classes.ChunkTensor and
 // torch.ops.dgs_ops.* with the reference's schemas (src/pybind.cc:11-38,
 // src/cuda/dgs_ops.h:10-50), implemented as a thin host layer over the C ABI
-// of include/dgs_b200.h.  This is the only file that sees torch types; every
-// kernel launch goes through an extern "C" entry point.
+// of include/dgs_b200.h.  Only this directory (binding/) sees torch types; every
+// kernel launch goes through an extern "C" entry point.  chunk_tensor.h holds the
+// ChunkTensor class, host_words.h the pinned size / status words leased per call,
+// pipeline.h the BlockPipeline class (several mini-batches in flight).
 //
 // Conventions kept from the reference: one process per GPU, tensors returned
 // on the current CUDA device, ChunkTensor construction/destruction collective
@@ -12,7 +14,6 @@
 // is also torch's default), and every failure surfaces as a c10::Error --
 // nothing calls exit()/abort() (src/dgs_headers.h:11-45).
 #include <ATen/cuda/CUDAContext.h>
-#include <ATen/cuda/CUDAGeneratorImpl.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <cuda_runtime.h>
@@ -26,107 +27,12 @@
 #include <vector>
 
 #include "../../../include/dgs_b200.h"
+#include "chunk_tensor.h"
+#include "host_words.h"
+#include "pipeline.h"
 
 namespace dgs {
 namespace {
-
-#define DGS_CHECK_RC(expr)                                                        \
-  do {                                                                            \
-    int rc__ = (expr);                                                            \
-    TORCH_CHECK(rc__ == DGS_OK, "dgs: ", dgs_last_error(), " (code ", rc__, ")"); \
-  } while (0)
-
-#define CHECK_CUDA(x) TORCH_CHECK((x).device().is_cuda(), #x " must be a CUDA tensor")
-
-// ---- pinned words the kernels write data-dependent sizes / status into ----
-struct HostWords {
-  int64_t* sizes = nullptr;        // [8]
-  int32_t* status = nullptr;       // [1]
-  int64_t* block_sizes = nullptr;  // [2 * DGS_MAX_HOPS]
-};
-
-HostWords& host_words() {
-  static HostWords w;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    TORCH_CHECK(cudaHostAlloc(&p, 256, cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess,
-                "dgs: cannot allocate pinned status words");
-    std::memset(p, 0, 256);
-    w.sizes = static_cast<int64_t*>(p);
-    w.status = reinterpret_cast<int32_t*>(static_cast<char*>(p) + 64);
-    w.block_sizes = reinterpret_cast<int64_t*>(static_cast<char*>(p) + 128);
-    static_assert(2 * DGS_MAX_HOPS * sizeof(int64_t) <= 128, "block sizes do not fit");
-  });
-  return w;
-}
-
-// Out-of-range ids / full tables are recorded by the kernels instead of
-// trapping; report them at the next point where the host looks.
-void check_status(const char* where) {
-  HostWords& w = host_words();
-  const int32_t st = *static_cast<volatile int32_t*>(w.status);
-  if (st != 0) {
-    *w.status = 0;
-    TORCH_CHECK(false, "dgs: a kernel reported ",
-                st == DGS_ERR_RANGE ? "an out-of-range id"
-                                    : (st == DGS_ERR_TABLE_FULL ? "a full hash table" : "an error"),
-                " (code ", st, "), noticed in ", where);
-  }
-}
-
-cudaStream_t current_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
-
-// Data-dependent sizes: the host marks a pinned word as pending, a kernel early
-// in the operator's sequence overwrites it, and the host picks the value up as
-// soon as it lands -- the kernels enqueued behind that one keep running while
-// the operator returns (the reference stalls on a blocking device read in the
-// middle of its sequence instead: src/cuda/rowwise_sampling.cu:147,
-// src/cuda/tensor_reindex.cu:129).
-constexpr int64_t kPending = INT64_MIN;
-
-int64_t wait_size(volatile int64_t* word, cudaStream_t stream, const char* where) {
-  for (uint64_t spins = 1;; ++spins) {
-    int64_t v = *word;
-    if (v != kPending) return v;
-    if ((spins & 0x3FF) == 0) {
-      // also the way out if the stream died: never spin on a value that cannot arrive
-      const cudaError_t q = cudaStreamQuery(stream);
-      if (q == cudaSuccess) {
-        v = *word;
-        TORCH_CHECK(v != kPending, "dgs: ", where, ": the stream finished without reporting a size");
-        return v;
-      }
-      TORCH_CHECK(q == cudaErrorNotReady, "dgs: ", where, ": CUDA error while waiting: ", cudaGetErrorString(q));
-    }
-#if defined(__x86_64__)
-    __builtin_ia32_pause();
-#endif
-  }
-}
-
-void sync_stream() {
-  TORCH_CHECK(cudaStreamSynchronize(current_stream()) == cudaSuccess, "dgs: stream synchronisation failed: ",
-              cudaGetErrorString(cudaGetLastError()));
-}
-
-bool is_id64(const torch::Tensor& t, const char* what) {
-  TORCH_CHECK(t.scalar_type() == torch::kInt64 || t.scalar_type() == torch::kInt32,
-              "ID can only be int32 or int64 (", what, ")");
-  return t.scalar_type() == torch::kInt64;
-}
-
-size_t dtype_size(torch::ScalarType t) {
-  // the types ChunkTensor accepts (src/chunk_tensor.cc:15-30)
-  switch (t) {
-    case torch::kInt32: return 4;
-    case torch::kInt64: return 8;
-    case torch::kFloat: return 4;
-    case torch::kDouble: return 8;
-    case torch::kBool: return 1;
-    default: TORCH_CHECK(false, "ChunkTensor: unsupported dtype ", t);
-  }
-}
 
 dgs_chunk_desc plain_desc(const torch::Tensor& t) {
   dgs_chunk_desc d;
@@ -139,145 +45,12 @@ dgs_chunk_desc plain_desc(const torch::Tensor& t) {
   return d;
 }
 
-torch::Tensor byte_scratch(size_t bytes, const torch::Device& dev) {
-  return torch::empty({static_cast<int64_t>(bytes)}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
-}
-
-// Visiting a request in address order (dgs_locality_order) is opt-in:
-// DGS_LOCALITY_ORDER=1.  It only pays when address translation limits the
-// request; with chunks allocated in 2 MB units (store.cc) peer reads run at the
-// NVLink rate unordered and the ordering pass would cost a few percent.
-bool wants_locality_order(const dgs_chunk_desc& d, int64_t n) {
-  static const char* env = std::getenv("DGS_LOCALITY_ORDER");
-  (void)d;
-  return env != nullptr && env[0] == '1' && n >= 2 && n <= 0xFFFFFFFFll;
-}
-
-// order tensor (uint32 positions, stored as int32) for `ids`, or an undefined tensor
-torch::Tensor make_locality_order(const dgs_chunk_desc& d, const torch::Tensor& ids, bool ids64, int64_t id_space,
-                                  cudaStream_t stream) {
-  const int64_t n = ids.numel();
-  if (!wants_locality_order(d, n)) return torch::Tensor();
-  torch::Tensor order = torch::empty({n}, torch::TensorOptions().dtype(torch::kInt32).device(ids.device()));
-  const size_t sb = dgs_locality_order_scratch_bytes();
-  torch::Tensor scratch = byte_scratch(sb, ids.device());
-  DGS_CHECK_RC(dgs_locality_order(ids.data_ptr(), ids64, n, std::max<int64_t>(id_space, 1),
-                                  static_cast<uint32_t*>(order.data_ptr()), scratch.data_ptr(), sb, stream));
-  return order;
-}
-
-// (seed, offset) from torch's default CUDA generator, so torch.manual_seed
-// controls sampling; a call that needs `streams` independent random streams uses
-// offset, offset + 1, ... and the generator moves past them.
-std::pair<uint64_t, uint64_t> next_rng(uint64_t streams = 1) {
-  auto gen = at::get_generator_or_default<at::CUDAGeneratorImpl>(
-      c10::nullopt, at::cuda::detail::getDefaultCUDAGenerator());
-  std::lock_guard<std::mutex> lock(gen->mutex_);
-  const uint64_t seed = gen->current_seed();
-  const uint64_t offset = gen->get_offset();
-  gen->set_offset(offset + 4 * ((streams + 3) / 4));  // torch keeps the offset a multiple of 4
-  return {seed, offset};
+void sync_stream() {
+  TORCH_CHECK(cudaStreamSynchronize(current_stream()) == cudaSuccess, "dgs: stream synchronisation failed: ",
+              cudaGetErrorString(cudaGetLastError()));
 }
 
 }  // namespace
-
-// ===========================================================================
-class ChunkTensor : public torch::CustomClassHolder {
- public:
-  ChunkTensor(std::vector<int64_t> shapes, torch::ScalarType dtype, int64_t capacity_per_gpu) {
-    TORCH_CHECK(shapes.size() == 1 || shapes.size() == 2, "ChunkTensor: shape must have 1 or 2 dims");
-    TORCH_CHECK(capacity_per_gpu >= 0, "ChunkTensor: capacity_per_gpu must be >= 0");
-    dtype_ = dtype;
-    const size_t esz = dtype_size(dtype);
-    DGS_CHECK_RC(dgs_device_check());
-    DGS_CHECK_RC(dgs_store_create(shapes.data(), static_cast<int32_t>(shapes.size()),
-                                  static_cast<int32_t>(esz), capacity_per_gpu, &store_));
-    DGS_CHECK_RC(dgs_store_desc(store_, &desc_));
-    elem_stride_ = dgs_store_elem_stride(store_);
-    TORCH_CHECK(cudaGetDevice(&device_) == cudaSuccess, "ChunkTensor: no current CUDA device");
-  }
-  ~ChunkTensor() override {
-    if (store_ != nullptr) dgs_store_destroy(store_);
-  }
-
-  torch::Tensor GetHostTensor() {
-    void* p = nullptr;
-    int64_t n = 0;
-    DGS_CHECK_RC(dgs_store_host_view(store_, &p, &n));
-    auto opt = torch::TensorOptions().device(torch::kCPU).dtype(dtype_);
-    return n > 0 ? torch::from_blob(p, {n}, opt) : torch::empty({0}, opt);
-  }
-
-  torch::Tensor GetSubDeviceTensor() {
-    void* p = nullptr;
-    int64_t n = 0;
-    DGS_CHECK_RC(dgs_store_local_view(store_, &p, &n));
-    auto opt = torch::TensorOptions().device(torch::Device(torch::kCUDA, device_)).dtype(dtype_);
-    return n > 0 ? torch::from_blob(p, {n}, opt) : torch::empty({0}, opt);
-  }
-
-  torch::Tensor IndexClass(torch::Tensor index, int32_t location_class) {
-    CHECK_CUDA(index);
-    check_status("_CAPI_index");
-    const bool ids64 = is_id64(index, "index");
-    c10::cuda::CUDAGuard guard(index.device());
-    index = index.contiguous();
-    const int64_t n = index.numel();
-    torch::Tensor out =
-        torch::empty({n, elem_stride_}, torch::TensorOptions().dtype(dtype_).device(index.device()));
-    torch::Tensor order =
-        make_locality_order(desc_, index, ids64, desc_.total / std::max<int64_t>(elem_stride_, 1), current_stream());
-    DGS_CHECK_RC(dgs_gather_rows(&desc_, location_class, index.data_ptr(), ids64, n, elem_stride_, out.data_ptr(),
-                                 order.defined() ? static_cast<const uint32_t*>(order.data_ptr()) : nullptr,
-                                 host_words().status, current_stream()));
-    return out;
-  }
-  torch::Tensor Index(torch::Tensor index) { return IndexClass(index, DGS_CLASS_ANY); }
-  torch::Tensor LocalIndex(torch::Tensor index) { return IndexClass(index, DGS_CLASS_LOCAL); }
-  torch::Tensor RemoteIndex(torch::Tensor index) { return IndexClass(index, DGS_CLASS_REMOTE); }
-  torch::Tensor HostIndex(torch::Tensor index) { return IndexClass(index, DGS_CLASS_HOST); }
-
-  std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> SplitIndex(torch::Tensor index) {
-    CHECK_CUDA(index);
-    check_status("_CAPI_split_index");
-    const bool ids64 = is_id64(index, "index");
-    c10::cuda::CUDAGuard guard(index.device());
-    index = index.contiguous().view({-1});
-    const int64_t n = index.numel();
-    torch::Tensor out = torch::empty_like(index);
-    const size_t sb = dgs_split_index_scratch_bytes(n);
-    torch::Tensor scratch = byte_scratch(sb, index.device());
-    int64_t* counts = host_words().sizes + 4;
-    DGS_CHECK_RC(dgs_split_index(&desc_, index.data_ptr(), ids64, n, elem_stride_, out.data_ptr(), counts,
-                                 scratch.data_ptr(), sb, current_stream()));
-    sync_stream();
-    const int64_t nl = counts[0], nr = counts[1], nh = counts[2];
-    TORCH_CHECK(nl + nr + nh == n, "dgs: split_index lost ids");
-    return std::make_tuple(out.narrow(0, 0, nl), out.narrow(0, nl, nr), out.narrow(0, nl + nr, nh));
-  }
-
-  void LoadFromTensor(torch::Tensor data) {
-    // argument checks of src/chunk_tensor.cc:174-181
-    dgs_chunk_desc d = desc_;
-    TORCH_CHECK(data.device().is_cpu(), "_CAPI_load_from_tensor: data must be a CPU tensor");
-    TORCH_CHECK(data.scalar_type() == dtype_, "_CAPI_load_from_tensor: dtype mismatch");
-    TORCH_CHECK(data.is_contiguous(), "_CAPI_load_from_tensor: data must be contiguous");
-    TORCH_CHECK(data.numel() == d.total, "_CAPI_load_from_tensor: shape mismatch");
-    TORCH_CHECK(data.dim() == 1 || (data.dim() == 2 && data.size(1) == elem_stride_),
-                "_CAPI_load_from_tensor: shape mismatch");
-    DGS_CHECK_RC(dgs_store_load(store_, data.data_ptr(), data.numel()));
-  }
-
-  const dgs_chunk_desc& desc() const { return desc_; }
-  torch::ScalarType dtype() const { return dtype_; }
-
- private:
-  dgs_store* store_ = nullptr;
-  dgs_chunk_desc desc_;
-  torch::ScalarType dtype_;
-  int64_t elem_stride_ = 1;
-  int device_ = 0;
-};
 
 // ===========================================================================
 // sampling
@@ -292,7 +65,6 @@ std::tuple<torch::Tensor, torch::Tensor> sample_impl(torch::Tensor seeds, const 
                                                       torch::ScalarType indices_dtype,
                                                       const dgs_chunk_desc* probs, int64_t k, bool replace) {
   CHECK_CUDA(seeds);
-  check_status("sample_neighbors");
   TORCH_CHECK(k >= 0, "num_picks must be >= 0");
   const bool ids64 = is_id64(seeds, "seeds");
   TORCH_CHECK(seeds.scalar_type() == indptr_dtype && seeds.scalar_type() == indices_dtype,
@@ -302,26 +74,23 @@ std::tuple<torch::Tensor, torch::Tensor> sample_impl(torch::Tensor seeds, const 
   const int64_t n = seeds.numel();
   auto opt = seeds.options();
   cudaStream_t stream = current_stream();
-  HostWords& w = host_words();
+  const Lease w("_CAPI_sample_neighbors*", seeds.device().index(), stream);
   const auto rng = next_rng();
 
   const size_t pb = dgs_sample_plan_bytes(n);
   torch::Tensor plan = byte_scratch(pb, seeds.device());
-  // CSC rows are stored in node order, so ordering the seeds by id orders the reads of `indices`
-  torch::Tensor order_t = make_locality_order(indices, seeds, ids64, indptr.total - 1, stream);
-  const uint32_t* order = order_t.defined() ? static_cast<const uint32_t*>(order_t.data_ptr()) : nullptr;
   const int64_t esz = ids64 ? 8 : 4;
   const bool one_shot = n * k * 2 * esz <= kOneShotOutputBytes;
 
   auto run = [&](torch::Tensor& row, torch::Tensor& col, int64_t cap, int64_t* nnz) {
     if (probs == nullptr)
-      DGS_CHECK_RC(dgs_sample_uniform(&indices, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), order,
+      DGS_CHECK_RC(dgs_sample_uniform(&indices, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(),
                                       rng.first, rng.second, row.data_ptr(), col.data_ptr(), cap, nnz,
-                                      nullptr, w.status, stream));
+                                      nullptr, w.status(), stream));
     else
       DGS_CHECK_RC(dgs_sample_weighted(&indices, probs, seeds.data_ptr(), ids64, n, k, replace,
-                                       plan.data_ptr(), order, rng.first, rng.second, row.data_ptr(),
-                                       col.data_ptr(), cap, nnz, nullptr, w.status, stream));
+                                       plan.data_ptr(), rng.first, rng.second, row.data_ptr(),
+                                       col.data_ptr(), cap, nnz, nullptr, w.status(), stream));
   };
 
   torch::Tensor row, col;
@@ -332,23 +101,25 @@ std::tuple<torch::Tensor, torch::Tensor> sample_impl(torch::Tensor seeds, const 
     const int64_t cap = n * k;
     row = torch::empty({cap}, opt);
     col = torch::empty({cap}, opt);
-    w.sizes[0] = kPending;
-    DGS_CHECK_RC(dgs_sample_plan(&indptr, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), w.sizes,
-                                 w.status, stream));
+    w.sizes()[0] = kPending;
+    DGS_CHECK_RC(dgs_sample_plan(&indptr, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), w.sizes(),
+                                 w.status(), stream));
     run(row, col, cap, nullptr);
-    nnz = wait_size(w.sizes, stream, "sample_neighbors");
-    check_status("sample_neighbors");
+    nnz = wait_size(w.sizes(), stream, "sample_neighbors");
+    if (strict_status()) sync_stream();
+    w.check();
     TORCH_CHECK(nnz >= 0 && nnz <= cap, "dgs: sampler returned an impossible size");
     return std::make_tuple(row.narrow(0, 0, nnz), col.narrow(0, 0, nnz));
   }
-  DGS_CHECK_RC(dgs_sample_plan(&indptr, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), w.sizes,
-                               w.status, stream));
+  DGS_CHECK_RC(dgs_sample_plan(&indptr, seeds.data_ptr(), ids64, n, k, replace, plan.data_ptr(), w.sizes(),
+                               w.status(), stream));
   sync_stream();
-  nnz = w.sizes[0];
-  check_status("sample_neighbors");
+  nnz = w.sizes()[0];
+  w.check();
   row = torch::empty({nnz}, opt);
   col = torch::empty({nnz}, opt);
   run(row, col, nnz, nullptr);
+  w.finish();
   return std::make_tuple(row, col);
 }
 
@@ -426,7 +197,6 @@ std::tuple<torch::Tensor, std::vector<torch::Tensor>> TensorRelabelCUDA(
   TORCH_CHECK(!mapping_tensors.empty(), "_CAPI_tensor_relabel: no mapping tensors");
   const torch::Tensor& first = mapping_tensors[0];
   CHECK_CUDA(first);
-  check_status("_CAPI_tensor_relabel");
   const bool ids64 = is_id64(first, "mapping tensors");
   for (const auto& t : mapping_tensors)
     TORCH_CHECK(t.device() == first.device() && t.scalar_type() == first.scalar_type(),
@@ -436,7 +206,7 @@ std::tuple<torch::Tensor, std::vector<torch::Tensor>> TensorRelabelCUDA(
                 "_CAPI_tensor_relabel: all tensors must share device and id type");
   c10::cuda::CUDAGuard guard(first.device());
   cudaStream_t stream = current_stream();
-  HostWords& w = host_words();
+  const Lease w("_CAPI_tensor_relabel", first.device().index(), stream);
 
   std::vector<torch::Tensor> keep;
   const dgs_segments keys = make_segments(mapping_tensors, keep);
@@ -456,12 +226,13 @@ std::tuple<torch::Tensor, std::vector<torch::Tensor>> TensorRelabelCUDA(
   torch::Tensor out = torch::empty({n_req}, first.options());
   // the count kernel reports the number of distinct keys; the numbering and
   // lookup kernels behind it are still in flight when this returns
-  w.sizes[1] = kPending;
-  DGS_CHECK_RC(dgs_unique_first_occurrence(&keys, ids64, table.data_ptr(), tb, uniq.data_ptr(), w.sizes + 1,
-                                           w.status, stream));
+  w.sizes()[0] = kPending;
+  DGS_CHECK_RC(dgs_unique_first_occurrence(&keys, ids64, table.data_ptr(), tb, uniq.data_ptr(), w.sizes(),
+                                           w.status(), stream));
   DGS_CHECK_RC(dgs_relabel_lookup(table.data_ptr(), tb, n_keys, &req, ids64, out.data_ptr(), stream));
-  const int64_t nu = wait_size(w.sizes + 1, stream, "_CAPI_tensor_relabel");
-  check_status("_CAPI_tensor_relabel");
+  const int64_t nu = wait_size(w.sizes(), stream, "_CAPI_tensor_relabel");
+  if (strict_status()) sync_stream();
+  w.check();
   TORCH_CHECK(nu >= 0 && nu <= n_keys, "dgs: relabel returned an impossible size");
   return std::make_tuple(uniq.narrow(0, 0, nu), out.split_with_sizes(split_sizes, 0));
 }
@@ -482,7 +253,6 @@ BlocksResult blocks_impl(torch::Tensor seeds, const dgs_chunk_desc& indptr, torc
                          const dgs_chunk_desc& indices, torch::ScalarType indices_dtype,
                          const dgs_chunk_desc* probs, const std::vector<int64_t>& fanouts, bool replace) {
   CHECK_CUDA(seeds);
-  check_status("sample_blocks");
   const bool ids64 = is_id64(seeds, "seeds");
   TORCH_CHECK(seeds.scalar_type() == indptr_dtype && seeds.scalar_type() == indices_dtype,
               "seeds, indptr and indices must share one id type");
@@ -530,7 +300,7 @@ BlocksResult blocks_impl(torch::Tensor seeds, const dgs_chunk_desc& indptr, torc
 
   auto opt = seeds.options();
   cudaStream_t stream = current_stream();
-  HostWords& w = host_words();
+  const Lease w("_CAPI_sample_blocks*", seeds.device().index(), stream);
   const auto rng = next_rng(static_cast<uint64_t>(H));
   torch::Tensor ws = byte_scratch(ws_bytes, seeds.device());
   std::vector<torch::Tensor> fr(H);
@@ -542,15 +312,15 @@ BlocksResult blocks_impl(torch::Tensor seeds, const dgs_chunk_desc& indptr, torc
     hops[h].coo_row = rows[H - 1 - h].data_ptr();
     hops[h].coo_col = cols[H - 1 - h].data_ptr();
     hops[h].frontier = fr[h].data_ptr();
-    w.block_sizes[2 * h] = w.block_sizes[2 * h + 1] = kPending;
+    w.sizes()[2 * h] = w.sizes()[2 * h + 1] = kPending;
   }
   DGS_CHECK_RC(dgs_sample_blocks(&indptr, &indices, probs, seeds.data_ptr(), ids64, hops, H, replace, rng.first,
-                                 rng.second, ws.data_ptr(), ws_bytes, w.block_sizes, w.status, stream));
+                                 rng.second, ws.data_ptr(), ws_bytes, w.sizes(), w.status(), stream));
   // the one read-back: the last size lands while that hop's numbering and lookup still run
   int64_t n_dst = n;
   for (int h = 0; h < H; ++h) {
-    const int64_t nnz = wait_size(w.block_sizes + 2 * h, stream, "sample_blocks");
-    const int64_t nu = wait_size(w.block_sizes + 2 * h + 1, stream, "sample_blocks");
+    const int64_t nnz = wait_size(w.sizes() + 2 * h, stream, "sample_blocks");
+    const int64_t nu = wait_size(w.sizes() + 2 * h + 1, stream, "sample_blocks");
     TORCH_CHECK(nnz >= 0 && nnz <= hops[h].seed_bound * hops[h].fanout && nu >= 0,
                 "dgs: sample_blocks returned an impossible size");
     const int at = H - 1 - h;
@@ -560,7 +330,8 @@ BlocksResult blocks_impl(torch::Tensor seeds, const dgs_chunk_desc& indptr, torc
     shape[2 * at + 1] = n_dst;
     n_dst = shape[2 * at];
   }
-  check_status("sample_blocks");
+  if (strict_status()) sync_stream();
+  w.check();
   frontier = fr[H - 1].narrow(0, 0, n_dst);
   return std::make_tuple(frontier, rows, cols, shape);
 }
@@ -616,7 +387,6 @@ std::tuple<torch::Tensor, torch::Tensor> CreateHashMapTensorCUDA(torch::Tensor i
                                                                  torch::Tensor input_value) {
   CHECK_CUDA(input_key);
   CHECK_CUDA(input_value);
-  check_status("_CAPI_create_hash_map");
   const bool ids64 = is_id64(input_key, "input_key");
   TORCH_CHECK(input_value.scalar_type() == input_key.scalar_type(), "key and value must share one id type");
   TORCH_CHECK(input_value.numel() == input_key.numel(), "key and value must have the same length");
@@ -627,8 +397,10 @@ std::tuple<torch::Tensor, torch::Tensor> CreateHashMapTensorCUDA(torch::Tensor i
   const int64_t slots = dgs_cache_table_slots(n);
   torch::Tensor kb = torch::empty({slots}, input_key.options());
   torch::Tensor vb = torch::empty({slots}, input_value.options());
+  const Lease w("_CAPI_create_hash_map", input_key.device().index(), current_stream());
   DGS_CHECK_RC(dgs_cache_build(input_key.data_ptr(), input_value.data_ptr(), ids64, n, kb.data_ptr(),
-                               vb.data_ptr(), slots, host_words().status, current_stream()));
+                               vb.data_ptr(), slots, w.status(), current_stream()));
+  w.finish();
   return std::make_tuple(kb, vb);
 }
 
@@ -638,7 +410,6 @@ torch::Tensor fetch_impl(torch::Tensor cpu_data, const dgs_chunk_desc& gpu, torc
   CHECK_CUDA(nid);
   CHECK_CUDA(hk);
   CHECK_CUDA(hv);
-  check_status("_CAPI_fetch_data");
   TORCH_CHECK(cpu_data.dim() == 2 && cpu_data.is_contiguous(), "cpu_data must be a contiguous 2-D tensor");
   TORCH_CHECK(cpu_data.is_cuda() || cpu_data.is_pinned(),
               "cpu_data must be pinned (page-locked) so that the GPU can read it in place");
@@ -650,9 +421,11 @@ torch::Tensor fetch_impl(torch::Tensor cpu_data, const dgs_chunk_desc& gpu, torc
   nid = nid.contiguous();
   const int64_t n = nid.numel(), D = cpu_data.size(1);
   torch::Tensor out = torch::empty({n, D}, torch::TensorOptions().dtype(gpu_dtype).device(nid.device()));
+  const Lease w("_CAPI_fetch_data*", nid.device().index(), current_stream());
   DGS_CHECK_RC(dgs_cache_fetch(cpu_data.data_ptr(), cpu_data.size(0), &gpu, nid.data_ptr(), ids64, n, D,
-                               hk.data_ptr(), hv.data_ptr(), hk.numel(), out.data_ptr(), host_words().status,
+                               hk.data_ptr(), hv.data_ptr(), hk.numel(), out.data_ptr(), w.status(),
                                current_stream()));
+  w.finish();
   return out;
 }
 }  // namespace
@@ -703,6 +476,15 @@ TORCH_LIBRARY(dgs_classes, m) {
       .def("_CAPI_remote_index", &ChunkTensor::RemoteIndex)
       .def("_CAPI_host_index", &ChunkTensor::HostIndex)
       .def("_CAPI_load_from_tensor", &ChunkTensor::LoadFromTensor);
+  // addition (no counterpart in src/pybind.cc): mini-batches in flight, see pipeline.h
+  m.class_<BlockPipeline>("BlockPipeline")
+      .def(torch::init<c10::intrusive_ptr<ChunkTensor>, c10::intrusive_ptr<ChunkTensor>,
+                       c10::optional<c10::intrusive_ptr<ChunkTensor>>, c10::optional<c10::intrusive_ptr<ChunkTensor>>,
+                       std::vector<int64_t>, bool, int64_t, int64_t>())
+      .def("submit", &BlockPipeline::submit)
+      .def("next", &BlockPipeline::next)
+      .def("pending", &BlockPipeline::pending)
+      .def("depth", &BlockPipeline::depth);
 }
 
 TORCH_LIBRARY(dgs_ops, m) {

@@ -1,0 +1,276 @@
+// torch.classes.dgs_classes.BlockPipeline: mini-batches in flight.
+//
+// The reference overlaps the sampling of the next mini-batches with the work on
+// the current one through DGL's DataLoader wrapped around ChunkTensorSampler
+// (oppo_bench/single_node/chunktensor.py:120-172, utils/chunktensor_sampler.py:63-118);
+// inside one batch its operators still stop at every size read-back.  This class
+// is that loader's role in native form, without DGL: `depth` slots, each with its
+// own CUDA stream, pinned size / status words, workspace and output buffers that
+// are allocated once for the largest batch.  submit(seeds) queues the whole
+// multi-hop sample + relabel sequence (dgs_sample_blocks) and, when a feature
+// table was given, the feature gather of the resulting input nodes directly behind
+// it (dgs_gather_rows_counted takes the row count from the device), all on the
+// slot's stream and without the host reading anything back.  next() hands out the
+// oldest batch: it waits for that batch's sizes (normally there already), makes
+// the caller's current stream wait for the slot's stream, and returns views of the
+// slot's buffers.  With two or more batches submitted ahead, the latency-bound
+// kernels of one batch's small hops run while another batch's gather keeps the
+// memory system (HBM, NVLink, host link) busy.
+//
+// Lifetime of the results: views into the slot, valid until the slot is submitted
+// to again, i.e. for `depth` - 1 further submit() calls.  A submit() first makes
+// the slot's stream wait for everything queued so far on the caller's current
+// stream, so consumers that were launched there before that submit() are safe.
+//
+// No counterpart in src/pybind.cc: an addition like the _CAPI_sample_blocks*
+// operators, built from the same C ABI calls.
+#pragma once
+#include <ATen/cuda/CUDAGeneratorImpl.h>
+
+#include "chunk_tensor.h"
+
+namespace dgs {
+
+// (seed, offset) from torch's default CUDA generator, so torch.manual_seed
+// controls sampling; a call that needs `streams` independent random streams uses
+// offset, offset + 1, ... and the generator moves past them.
+inline std::pair<uint64_t, uint64_t> next_rng(uint64_t streams = 1) {
+  auto gen = at::get_generator_or_default<at::CUDAGeneratorImpl>(
+      c10::nullopt, at::cuda::detail::getDefaultCUDAGenerator());
+  std::lock_guard<std::mutex> lock(gen->mutex_);
+  const uint64_t seed = gen->current_seed();
+  const uint64_t offset = gen->get_offset();
+  gen->set_offset(offset + 4 * ((streams + 3) / 4));  // torch keeps the offset a multiple of 4
+  return {seed, offset};
+}
+
+using PipelineResult = std::tuple<torch::Tensor, std::vector<torch::Tensor>, std::vector<torch::Tensor>,
+                                  std::vector<int64_t>, torch::Tensor>;
+
+class BlockPipeline : public torch::CustomClassHolder {
+ public:
+  BlockPipeline(c10::intrusive_ptr<ChunkTensor> indptr, c10::intrusive_ptr<ChunkTensor> indices,
+                c10::optional<c10::intrusive_ptr<ChunkTensor>> probs,
+                c10::optional<c10::intrusive_ptr<ChunkTensor>> features, std::vector<int64_t> fanouts,
+                bool replace, int64_t max_seeds, int64_t depth)
+      : indptr_(std::move(indptr)), indices_(std::move(indices)), replace_(replace), max_seeds_(max_seeds) {
+    if (probs.has_value() && probs.value().defined()) probs_ = probs.value();
+    if (features.has_value() && features.value().defined()) features_ = features.value();
+    H_ = static_cast<int>(fanouts.size());
+    TORCH_CHECK(H_ >= 1 && H_ <= DGS_MAX_HOPS, "BlockPipeline: between 1 and ", DGS_MAX_HOPS, " fan-outs");
+    TORCH_CHECK(max_seeds >= 1, "BlockPipeline: max_seeds must be >= 1");
+    TORCH_CHECK(depth >= 1 && depth <= 16, "BlockPipeline: depth must be in 1..16");
+    for (int64_t k : fanouts) TORCH_CHECK(k >= 1, "BlockPipeline: fan-outs must be >= 1");
+    TORCH_CHECK(indptr_->dtype() == indices_->dtype() &&
+                    (indptr_->dtype() == torch::kInt64 || indptr_->dtype() == torch::kInt32),
+                "BlockPipeline: indptr and indices must share one id type (int32 or int64)");
+    TORCH_CHECK(!probs_.defined() || probs_->dtype() == torch::kFloat, "probs must be float32");
+    ids64_ = indptr_->dtype() == torch::kInt64;
+    device_ = indptr_->device();
+    // the reference applies the fan-outs last to first (chunktensor_sampler.py:97)
+    applied_.assign(fanouts.rbegin(), fanouts.rend());
+
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+    dgs_hop hops[DGS_MAX_HOPS];
+    DGS_CHECK_RC(dgs_sample_blocks_bounds(max_seeds_, applied_.data(), H_, indptr_->desc().total - 1, hops));
+    ws_bytes_ = dgs_sample_blocks_workspace_bytes(hops, H_);
+    const int64_t esz = ids64_ ? 8 : 4;
+    int64_t slot_bytes = static_cast<int64_t>(ws_bytes_) + max_seeds_ * esz;
+    for (int h = 0; h < H_; ++h) {
+      edge_cap_[h] = hops[h].seed_bound * hops[h].fanout;
+      frontier_cap_[h] = hops[h].frontier_bound;
+      slot_bytes += (2 * edge_cap_[h] + frontier_cap_[h]) * esz;
+    }
+    if (features_.defined())
+      slot_bytes += frontier_cap_[H_ - 1] * features_->elem_stride() * static_cast<int64_t>(dtype_size(features_->dtype()));
+    TORCH_CHECK(slot_bytes * depth <= kBudgetBytes, "BlockPipeline: ", depth, " slots of ", slot_bytes,
+                " bytes exceed the ", kBudgetBytes, "-byte budget; lower max_seeds, the fan-outs or depth");
+
+    const auto dev = torch::Device(torch::kCUDA, static_cast<c10::DeviceIndex>(device_));
+    const auto id_opt = torch::TensorOptions().dtype(indptr_->dtype()).device(dev);
+    slots_.resize(depth);
+    for (Slot& s : slots_) {
+      TORCH_CHECK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess,
+                  "BlockPipeline: cannot create a stream");
+      TORCH_CHECK(cudaEventCreateWithFlags(&s.ready, cudaEventDisableTiming) == cudaSuccess &&
+                      cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming) == cudaSuccess,
+                  "BlockPipeline: cannot create an event");
+      void* p = nullptr;
+      TORCH_CHECK(cudaHostAlloc(&p, 256, cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess,
+                  "BlockPipeline: cannot allocate pinned words");
+      std::memset(p, 0, 256);
+      s.sizes = static_cast<int64_t*>(p);
+      s.status = reinterpret_cast<int32_t*>(static_cast<char*>(p) + 2 * DGS_MAX_HOPS * sizeof(int64_t));
+      s.seeds = torch::empty({max_seeds_}, id_opt);
+      s.ws = byte_scratch(ws_bytes_, dev);
+      for (int h = 0; h < H_; ++h) {
+        s.rows.push_back(torch::empty({edge_cap_[h]}, id_opt));
+        s.cols.push_back(torch::empty({edge_cap_[h]}, id_opt));
+        s.frontier.push_back(torch::empty({frontier_cap_[h]}, id_opt));
+      }
+      if (features_.defined())
+        s.feats = torch::empty({frontier_cap_[H_ - 1], features_->elem_stride()},
+                               torch::TensorOptions().dtype(features_->dtype()).device(dev));
+    }
+    // the buffers were allocated on the current stream; nothing of theirs is pending there, but make the
+    // slots' streams start after whatever the allocator's stream still holds
+    TORCH_CHECK(cudaStreamSynchronize(current_stream()) == cudaSuccess, "BlockPipeline: synchronisation failed");
+  }
+
+  ~BlockPipeline() override {
+    for (Slot& s : slots_) {
+      if (s.stream != nullptr) cudaStreamSynchronize(s.stream);
+      if (s.ready != nullptr) cudaEventDestroy(s.ready);
+      if (s.done != nullptr) cudaEventDestroy(s.done);
+      if (s.stream != nullptr) cudaStreamDestroy(s.stream);
+      if (s.sizes != nullptr) cudaFreeHost(s.sizes);
+    }
+  }
+
+  // Queue one mini-batch.  `seeds`: 1-D ids of the graph's id type, at most max_seeds of them, on the
+  // pipeline's device or in (preferably pinned) host memory; they are copied into the slot, so the caller
+  // may reuse its tensor as soon as this returns and the current stream has moved on.
+  void submit(torch::Tensor seeds) {
+    TORCH_CHECK(in_flight_ < static_cast<int64_t>(slots_.size()),
+                "BlockPipeline.submit: all ", slots_.size(), " slots hold batches; call next() first");
+    TORCH_CHECK(seeds.scalar_type() == indptr_->dtype(), "seeds, indptr and indices must share one id type");
+    TORCH_CHECK(seeds.device().is_cpu() || (seeds.device().is_cuda() && seeds.device().index() == device_),
+                "BlockPipeline.submit: seeds must be on the pipeline's device or on the host");
+    seeds = seeds.contiguous().view({-1});
+    const int64_t n = seeds.numel();
+    TORCH_CHECK(n <= max_seeds_, "BlockPipeline.submit: ", n, " seeds, the pipeline was built for ", max_seeds_);
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+    Slot& s = slots_[head_ % slots_.size()];
+    report_late_status(s, "BlockPipeline.submit");
+    s.n_seeds = n;
+    s.batch = head_;
+    if (n > 0) {
+      // everything the caller queued so far (the seeds' producer, consumers of this slot's previous
+      // results) comes first
+      cudaStream_t cur = current_stream();
+      TORCH_CHECK(cudaEventRecord(s.ready, cur) == cudaSuccess && cudaStreamWaitEvent(s.stream, s.ready, 0) == cudaSuccess,
+                  "BlockPipeline.submit: cannot order the slot's stream after the current stream");
+      const size_t esz = ids64_ ? 8 : 4;
+      TORCH_CHECK(cudaMemcpyAsync(s.seeds.data_ptr(), seeds.data_ptr(), n * esz,
+                                  seeds.device().is_cpu() ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice,
+                                  s.stream) == cudaSuccess,
+                  "BlockPipeline.submit: copying the seeds failed: ", cudaGetErrorString(cudaGetLastError()));
+      dgs_hop hops[DGS_MAX_HOPS];
+      DGS_CHECK_RC(dgs_sample_blocks_bounds(n, applied_.data(), H_, indptr_->desc().total - 1, hops));
+      for (int h = 0; h < H_; ++h) {
+        hops[h].coo_row = s.rows[h].data_ptr();
+        hops[h].coo_col = s.cols[h].data_ptr();
+        hops[h].frontier = s.frontier[h].data_ptr();
+        s.edge_bound[h] = hops[h].seed_bound * hops[h].fanout;
+        s.frontier_bound[h] = hops[h].frontier_bound;
+        s.sizes[2 * h] = s.sizes[2 * h + 1] = kPending;
+      }
+      const auto rng = next_rng(static_cast<uint64_t>(H_));
+      DGS_CHECK_RC(dgs_sample_blocks(&indptr_->desc(), &indices_->desc(), probs_.defined() ? &probs_->desc() : nullptr,
+                                     s.seeds.data_ptr(), ids64_, hops, H_, replace_, rng.first, rng.second,
+                                     s.ws.data_ptr(), ws_bytes_, s.sizes, s.status, s.stream));
+      if (features_.defined()) {
+        const int64_t* n_dev = dgs_sample_blocks_frontier_count(hops, H_, s.ws.data_ptr());
+        TORCH_CHECK(n_dev != nullptr, "BlockPipeline.submit: no frontier count");
+        DGS_CHECK_RC(dgs_gather_rows_counted(&features_->desc(), s.frontier[H_ - 1].data_ptr(), ids64_,
+                                             s.frontier_bound[H_ - 1], n_dev, features_->elem_stride(),
+                                             s.feats.data_ptr(), s.status, s.stream));
+      }
+      TORCH_CHECK(cudaEventRecord(s.done, s.stream) == cudaSuccess, "BlockPipeline.submit: cannot record an event");
+    }
+    ++head_;
+    ++in_flight_;
+  }
+
+  // The oldest submitted batch: (input_nodes, coo_rows, coo_cols, [n_src_0, n_dst_0, n_src_1, ...], features)
+  // with the blocks in layer order, outermost hop first, exactly as _CAPI_sample_blocks* returns them;
+  // features is [len(input_nodes), D] (empty when the pipeline has no feature table).
+  PipelineResult next() {
+    TORCH_CHECK(in_flight_ > 0, "BlockPipeline.next: nothing was submitted");
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+    Slot& s = slots_[tail_ % slots_.size()];
+    std::vector<torch::Tensor> rows(H_), cols(H_);
+    std::vector<int64_t> shape(2 * H_);
+    torch::Tensor frontier, feats;
+    int64_t n_dst = s.n_seeds;
+    if (s.n_seeds == 0) {
+      for (int h = 0; h < H_; ++h) {
+        rows[h] = s.rows[0].narrow(0, 0, 0);
+        cols[h] = s.cols[0].narrow(0, 0, 0);
+      }
+      frontier = s.frontier[0].narrow(0, 0, 0);
+      if (features_.defined()) feats = s.feats.narrow(0, 0, 0);
+    } else {
+      for (int h = 0; h < H_; ++h) {
+        const int64_t nnz = wait_size(s.sizes + 2 * h, s.stream, "BlockPipeline.next");
+        const int64_t nu = wait_size(s.sizes + 2 * h + 1, s.stream, "BlockPipeline.next");
+        TORCH_CHECK(nnz >= 0 && nnz <= s.edge_bound[h] && nu >= 0, "dgs: BlockPipeline returned an impossible size");
+        const int at = H_ - 1 - h;
+        rows[at] = s.rows[h].narrow(0, 0, nnz);
+        cols[at] = s.cols[h].narrow(0, 0, nnz);
+        shape[2 * at] = std::min(nu, s.frontier_bound[h]);
+        shape[2 * at + 1] = n_dst;
+        n_dst = shape[2 * at];
+      }
+      if (strict_status())
+        TORCH_CHECK(cudaEventSynchronize(s.done) == cudaSuccess, "BlockPipeline.next: synchronisation failed");
+      const int32_t st = *static_cast<volatile int32_t*>(s.status);
+      if (st != 0) {
+        *s.status = 0;
+        ++tail_;
+        --in_flight_;
+        TORCH_CHECK(false, "dgs: BlockPipeline batch ", s.batch, ": a kernel reported ", status_text(st), " (code ",
+                    st, ")");
+      }
+      // the caller's stream sees the batch complete (sampling, relabelling and the feature gather)
+      TORCH_CHECK(cudaStreamWaitEvent(current_stream(), s.done, 0) == cudaSuccess,
+                  "BlockPipeline.next: cannot order the current stream after the slot's stream");
+      frontier = s.frontier[H_ - 1].narrow(0, 0, n_dst);
+      if (features_.defined()) feats = s.feats.narrow(0, 0, n_dst);
+    }
+    if (!feats.defined()) feats = torch::empty({0}, torch::TensorOptions().dtype(torch::kFloat).device(frontier.device()));
+    ++tail_;
+    --in_flight_;
+    return std::make_tuple(frontier, rows, cols, shape, feats);
+  }
+
+  int64_t pending() const { return in_flight_; }
+  int64_t depth() const { return static_cast<int64_t>(slots_.size()); }
+
+ private:
+  static constexpr int64_t kBudgetBytes = int64_t(32) << 30;
+
+  struct Slot {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ready = nullptr, done = nullptr;
+    int64_t* sizes = nullptr;   // [2 * DGS_MAX_HOPS], pinned
+    int32_t* status = nullptr;  // pinned
+    torch::Tensor seeds, ws, feats;
+    std::vector<torch::Tensor> rows, cols, frontier;  // indexed by hop of application
+    int64_t edge_bound[DGS_MAX_HOPS] = {0}, frontier_bound[DGS_MAX_HOPS] = {0};
+    int64_t n_seeds = 0, batch = -1;
+  };
+
+  // a status left by kernels that were still running when next() handed the batch out
+  static void report_late_status(Slot& s, const char* where) {
+    const int32_t st = *static_cast<volatile int32_t*>(s.status);
+    if (st != 0) {
+      *s.status = 0;
+      TORCH_CHECK(false, "dgs: a kernel of BlockPipeline batch ", s.batch, " reported ", status_text(st), " (code ", st,
+                  ") after next() had returned it; noticed in ", where);
+    }
+  }
+
+  c10::intrusive_ptr<ChunkTensor> indptr_, indices_, probs_, features_;
+  std::vector<int64_t> applied_;
+  bool replace_ = false, ids64_ = true;
+  int H_ = 0;
+  int device_ = 0;
+  int64_t max_seeds_ = 0;
+  size_t ws_bytes_ = 0;
+  int64_t edge_cap_[DGS_MAX_HOPS] = {0}, frontier_cap_[DGS_MAX_HOPS] = {0};
+  std::vector<Slot> slots_;
+  int64_t head_ = 0, tail_ = 0, in_flight_ = 0;
+};
+
+}  // namespace dgs

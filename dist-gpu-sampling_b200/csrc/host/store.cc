@@ -27,6 +27,7 @@
 
 #include <atomic>
 #include <cerrno>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -74,6 +75,14 @@ void tracked_free(void* p, size_t bytes) {
   if (p == nullptr) return;
   cudaFree(p);
   g_allocated -= static_cast<int64_t>(bytes);
+}
+
+// Host-side failure injection for the tests of the collective error path: with
+// DGS_TEST_REFUSE_HOST_REGISTER=<rank> in the environment that rank treats the pinning of the host tail
+// as refused by the OS.  Nothing on the GPU is touched; read at every call so a test can set and clear it.
+bool host_register_refused(int rank) {
+  const char* e = std::getenv("DGS_TEST_REFUSE_HOST_REGISTER");
+  return e != nullptr && e[0] != '\0' && std::atoi(e) == rank;
 }
 
 struct Meta {
@@ -220,8 +229,10 @@ extern "C" int dgs_store_create(const int64_t* shape, int32_t ndim, int32_t esz,
       }
     }
     if (rc == DGS_OK) {
-      cudaError_t e = cudaHostRegister(s->host, s->host_bytes, cudaHostRegisterDefault);
-      if (e != cudaSuccess) {
+      const bool refused = host_register_refused(s->rank);  // injected: as if pinning had failed for good
+      cudaError_t e = refused ? cudaErrorMemoryAllocation
+                              : cudaHostRegister(s->host, s->host_bytes, cudaHostRegisterDefault);
+      if (e != cudaSuccess && !refused) {
         // Seen on a 2-GPU run: pinning a 6.7 GB shared segment in one call failed with
         // cudaErrorOperatingSystem while several ranks were pinning the same pages.  Registering the
         // tail in 1 GiB pieces asks the OS for far less at a time; with UVA the pieces form one
@@ -267,6 +278,10 @@ extern "C" int dgs_store_create(const int64_t* shape, int32_t ndim, int32_t esz,
     if (rc == DGS_OK) {
       // same fill as the reference (src/chunk_tensor.cc:108)
       cudaError_t e = cudaMemset(s->dev[s->rank], 0xFF, s->local_bytes);
+      // the fill runs on the legacy default stream, the exchanges below on the communicator's own
+      // non-blocking stream: finish the fill here, so that nothing a peer writes into this chunk once the
+      // constructor has returned on its side (a root's LoadFromTensor, an in-place fill) can be overtaken by it
+      if (e == cudaSuccess) e = cudaDeviceSynchronize();
       if (e != cudaSuccess) rc = cuda_fail(e, "cudaMemset(chunk)", __FILE__, __LINE__);
     }
     if (s->world > 1) {
@@ -304,8 +319,21 @@ extern "C" int dgs_store_create(const int64_t* shape, int32_t ndim, int32_t esz,
     }
   }
   if (s->world > 1) {
-    int brc = dgs_comm_barrier();
-    if (rc == DGS_OK) rc = brc;
+    // The outcome is collective: a rank that failed in any stage above (pinning the host tail, allocating
+    // or exporting its chunk, opening a peer's) fails the constructor on every rank.  Without this an
+    // all-host tensor -- no handle exchange, so no `ok` flags -- could be alive on some ranks and not on
+    // others, and the survivors' next collective would wait for ever.  Doubles as the closing barrier.
+    int32_t verdicts[DGS_MAX_PARTS];
+    const int32_t v = rc;
+    const int rc2 = comm_allgather_bytes(&v, verdicts, sizeof(v));
+    if (rc == DGS_OK) rc = rc2;
+    if (rc == DGS_OK)
+      for (int i = 0; i < s->world; ++i)
+        if (verdicts[i] != DGS_OK) {
+          set_error("ChunkTensor creation failed on rank %d (code %d)", i, verdicts[i]);
+          rc = verdicts[i];
+          break;
+        }
   }
   if (rc != DGS_OK) {
     release_local(s);

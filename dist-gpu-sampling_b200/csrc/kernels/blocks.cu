@@ -99,6 +99,20 @@ extern "C" size_t dgs_sample_blocks_workspace_bytes(const dgs_hop* hops, int32_t
   return total;
 }
 
+extern "C" const int64_t* dgs_sample_blocks_frontier_count(const dgs_hop* hops, int32_t n_hops, void* workspace) {
+  using namespace dgs;
+  if (hops == nullptr || workspace == nullptr || n_hops < 1 || n_hops > DGS_MAX_HOPS) return nullptr;
+  // same walk as the carving in dgs_sample_blocks: the word sits in the last hop's table
+  char* p = static_cast<char*>(workspace) + WS_ALIGN;
+  for (int h = 0; h < n_hops; ++h) {
+    const int64_t key_bound = hops[h].seed_bound * (1 + hops[h].fanout);
+    p += ws_align(dgs_sample_plan_bytes(hops[h].seed_bound));
+    if (h == n_hops - 1) return unique_total(p, key_bound);
+    p += ws_align(dgs_relabel_table_bytes(key_bound));
+  }
+  return nullptr;
+}
+
 extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_desc* indices,
                                  const dgs_chunk_desc* probs, const void* seeds, int32_t ids64,
                                  const dgs_hop* hops, int32_t n_hops, int32_t replace, uint64_t rng_seed,
@@ -178,9 +192,9 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
     const uint64_t key = sample_rng_key(rng_seed, rng_offset + static_cast<uint64_t>(h));
     const bool row_is_position = h > 0;
     rc = probs != nullptr
-             ? launch_sample_weighted(*indices, *probs, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], nullptr,
+             ? launch_sample_weighted(*indices, *probs, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h],
                                       key, hp.coo_row, hp.coo_col, edge_bound, nullptr, row_is_position, status, s)
-             : launch_sample_uniform(*indices, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], nullptr, key,
+             : launch_sample_uniform(*indices, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], key,
                                      hp.coo_row, hp.coo_col, edge_bound, nullptr, row_is_position, status, s);
     if (rc != DGS_OK) return rc;
     const Count nnz{edge_bound, nnz_dev, nullptr};

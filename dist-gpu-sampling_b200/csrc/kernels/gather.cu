@@ -171,27 +171,30 @@ struct CachedRows {
 
 template <typename Src, int VEC, bool REALIGN>
 __global__ void __launch_bounds__(GATHER_BLOCK)
-gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int64_t D, const int sh,
-                   const uint32_t nvec, const uint32_t rows_per_tile, const uint32_t div_magic,
+gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n_bound, const int64_t* __restrict__ n_dev,
+                   const int64_t D, const int sh, const uint32_t nvec, const uint32_t rows_per_tile, const uint32_t div_magic,
                    const uint32_t slot_shift,
-                   char* __restrict__ out, const uint32_t* __restrict__ order,
-                   int32_t* __restrict__ status) {
+                   char* __restrict__ out, int32_t* __restrict__ status) {
   using V = typename VecT<VEC>::type;
   __shared__ const char* s_src[GATHER_MAX_ROWS];
-  __shared__ char* s_dst[GATHER_MAX_ROWS];  // only used with a processing order
   pdl_enter();
 
+  // the number of rows is the host's (n_dev == nullptr) or a device word written by an earlier kernel on
+  // the stream, with n_bound the upper limit the grid was sized for: CTAs past the live count leave at once
+  int64_t n = n_bound;
+  if (n_dev != nullptr) {
+    const int64_t live = *n_dev;
+    n = live < n_bound ? (live < 0 ? 0 : live) : n_bound;
+  }
   const int64_t tile_row0 = static_cast<int64_t>(blockIdx.x) * rows_per_tile;
+  if (tile_row0 >= n) return;
   const uint32_t rows_here =
       static_cast<uint32_t>(min(static_cast<int64_t>(rows_per_tile), n - tile_row0));
 
   // ---- phase 1: one resolution per row -------------------------------------
   bool any_special = false;
   for (uint32_t r = threadIdx.x; r < rows_here; r += GATHER_BLOCK) {
-    // with a processing order the r-th row of the tile is request position order[..]
-    const int64_t i = order != nullptr ? static_cast<int64_t>(order[tile_row0 + r]) : tile_row0 + r;
-    const char* src = rows.template locate<VEC, REALIGN>(i, status);
-    s_dst[r] = out + (i * D << sh);
+    const char* src = rows.template locate<VEC, REALIGN>(tile_row0 + r, status);
     any_special |= (reinterpret_cast<uintptr_t>(src) <= 1);
     s_src[r] = src;
   }
@@ -255,8 +258,7 @@ gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int6
       if (at[u] != ~0u) {
         const uint32_t r = rows_per_tile == 1 ? 0u : (at[u] >> 16);
         const uint32_t j = rows_per_tile == 1 ? at[u] : (at[u] & 0xFFFFu);
-        if (order == nullptr) out_tile[r * nvec + j] = v[u];
-        else reinterpret_cast<V*>(s_dst[r])[j] = v[u];
+        out_tile[r * nvec + j] = v[u];
       }
     }
   }
@@ -267,8 +269,8 @@ gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int6
     for (uint32_t r = 0; r < rows_here; ++r) {
       const char* src = s_src[r];
       if (reinterpret_cast<uintptr_t>(src) > 1) continue;
-      char* dst = s_dst[r];
-      const int64_t i = (dst - out) / (D << sh);  // request position of this row
+      const int64_t i = tile_row0 + r;  // request position of this row
+      char* dst = out + (i * D << sh);
       if (src == DGS_ROW_ZERO) {
         for (int64_t b = threadIdx.x; b < (D << sh); b += GATHER_BLOCK) dst[b] = 0;
       } else {
@@ -288,8 +290,9 @@ gather_rows_kernel(const __grid_constant__ Src rows, const int64_t n, const int6
 }
 
 template <typename Src, int VEC, bool REALIGN>
-int launch_gather_r(const Src& rows, int64_t n, int64_t D, int sh, void* out, const uint32_t* order,
-                    int32_t* status, cudaStream_t stream) {
+int launch_gather_r(const Src& rows, Count nc, int64_t D, int sh, void* out, int32_t* status,
+                    cudaStream_t stream) {
+  const int64_t n = nc.bound;
   const int64_t row_bytes = D << sh;
   const int64_t nvec64 = row_bytes / VEC;
   // the in-tile index q < rows*nvec must keep q*nvec < 2^32 for the magic divide
@@ -318,37 +321,37 @@ int launch_gather_r(const Src& rows, int64_t n, int64_t D, int sh, void* out, co
   const int64_t tiles = (n + rows_per_tile - 1) / rows_per_tile;
   DGS_REQUIRE(tiles <= 0x7fffffffLL, DGS_ERR_UNSUPPORTED, "gather: too many rows (%lld)", (long long)n);
   DGS_CUDA_TRY(launch_chained(SITE_GATHER, gather_rows_kernel<Src, VEC, REALIGN>, static_cast<unsigned>(tiles), GATHER_BLOCK, stream, rows,
-                              n, D, sh, nvec, rows_per_tile, magic, slot_shift, static_cast<char*>(out), order, status));
+                              n, nc.dev, D, sh, nvec, rows_per_tile, magic, slot_shift, static_cast<char*>(out), status));
   return DGS_OK;
 }
 
 // realign: some storage region starts rows off the vector boundary (see vector_copy_ok)
 template <typename Src, int VEC>
-int launch_gather(const Src& rows, bool realign, int64_t n, int64_t D, int sh, void* out, const uint32_t* order,
-                  int32_t* status, cudaStream_t stream) {
+int launch_gather(const Src& rows, bool realign, Count n, int64_t D, int sh, void* out, int32_t* status,
+                  cudaStream_t stream) {
   if constexpr (VEC >= 8) {
-    if (realign) return launch_gather_r<Src, VEC, true>(rows, n, D, sh, out, order, status, stream);
+    if (realign) return launch_gather_r<Src, VEC, true>(rows, n, D, sh, out, status, stream);
   }
-  return launch_gather_r<Src, VEC, false>(rows, n, D, sh, out, order, status, stream);
+  return launch_gather_r<Src, VEC, false>(rows, n, D, sh, out, status, stream);
 }
 
 template <typename Src>
-int dispatch_vec(int vec, bool realign, const Src& rows, int64_t n, int64_t D, int sh, void* out,
-                 const uint32_t* order, int32_t* status, cudaStream_t stream) {
+int dispatch_vec(int vec, bool realign, const Src& rows, Count n, int64_t D, int sh, void* out,
+                 int32_t* status, cudaStream_t stream) {
   switch (vec) {
-    case 16: return launch_gather<Src, 16>(rows, realign, n, D, sh, out, order, status, stream);
-    case 8: return launch_gather<Src, 8>(rows, realign, n, D, sh, out, order, status, stream);
-    case 4: return launch_gather<Src, 4>(rows, false, n, D, sh, out, order, status, stream);
-    case 2: return launch_gather<Src, 2>(rows, false, n, D, sh, out, order, status, stream);
-    default: return launch_gather<Src, 1>(rows, false, n, D, sh, out, order, status, stream);
+    case 16: return launch_gather<Src, 16>(rows, realign, n, D, sh, out, status, stream);
+    case 8: return launch_gather<Src, 8>(rows, realign, n, D, sh, out, status, stream);
+    case 4: return launch_gather<Src, 4>(rows, false, n, D, sh, out, status, stream);
+    case 2: return launch_gather<Src, 2>(rows, false, n, D, sh, out, status, stream);
+    default: return launch_gather<Src, 1>(rows, false, n, D, sh, out, status, stream);
   }
 }
 
 template <typename IdxT>
-int run_gather(int vec, bool realign, const dgs_chunk_desc& d, const void* idx, int64_t n, int64_t D, int sh,
-               void* out, const uint32_t* order, int32_t* status, cudaStream_t stream) {
+int run_gather(int vec, bool realign, const dgs_chunk_desc& d, const void* idx, Count n, int64_t D, int sh,
+               void* out, int32_t* status, cudaStream_t stream) {
   ChunkRows<IdxT> rows{d, static_cast<const IdxT*>(idx), D, d.total / D, sh};
-  return dispatch_vec(vec, realign, rows, n, D, sh, out, order, status, stream);
+  return dispatch_vec(vec, realign, rows, n, D, sh, out, status, stream);
 }
 
 // ---- cache table build -------------------------------------------------------
@@ -399,7 +402,7 @@ int run_cache_fetch(int vec, bool realign, const dgs_chunk_desc& gpu, const void
                         gpu.total / D,
                         cpu_rows,
                         sh};
-  return dispatch_vec(vec, realign, rows, n, D, sh, out, nullptr, status, stream);
+  return dispatch_vec(vec, realign, rows, exact_count(n), D, sh, out, status, stream);
 }
 
 // largest power of two <= 16 dividing x (x == 0 counts as "any")
@@ -463,25 +466,38 @@ int gather_vec_bytes(const dgs_chunk_desc& d, int64_t D, const void* out, bool* 
 
 }  // namespace dgs
 
-extern "C" int dgs_gather_rows(const dgs_chunk_desc* t, int32_t location_class, const void* idx,
-                               int32_t ids64, int64_t n, int64_t D, void* out, const uint32_t* order,
-                               int32_t* status, dgs_stream_t stream) {
-  using namespace dgs;
-  (void)location_class;  // hint only: the owner is resolved per row for every class
-  int rc = validate_desc(t, "dgs_gather_rows");
+namespace dgs {
+namespace {
+int gather_entry(const char* who, const dgs_chunk_desc* t, const void* idx, int32_t ids64, Count n, int64_t D,
+                 void* out, int32_t* status, dgs_stream_t stream) {
+  int rc = validate_desc(t, who);
   if (rc != DGS_OK) return rc;
-  DGS_REQUIRE(n >= 0 && D >= 1, DGS_ERR_INVALID, "dgs_gather_rows: n=%lld D=%lld", (long long)n,
-              (long long)D);
-  if (n == 0) return DGS_OK;
-  DGS_REQUIRE(idx != nullptr && out != nullptr, DGS_ERR_INVALID, "dgs_gather_rows: null buffer");
+  DGS_REQUIRE(n.bound >= 0 && D >= 1, DGS_ERR_INVALID, "%s: n=%lld D=%lld", who, (long long)n.bound, (long long)D);
+  if (n.bound == 0) return DGS_OK;
+  DGS_REQUIRE(idx != nullptr && out != nullptr, DGS_ERR_INVALID, "%s: null buffer", who);
   const int sh = esz_log2(t->esz);
   bool realign = false;
   const int vec = gather_vec_bytes(*t, D, out, &realign);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  DGS_REQUIRE(order == nullptr || n <= 0xFFFFFFFFll, DGS_ERR_UNSUPPORTED,
-              "dgs_gather_rows: a processing order covers at most 2^32 ids");
-  return ids64 ? run_gather<int64_t>(vec, realign, *t, idx, n, D, sh, out, order, status, s)
-               : run_gather<int32_t>(vec, realign, *t, idx, n, D, sh, out, order, status, s);
+  return ids64 ? run_gather<int64_t>(vec, realign, *t, idx, n, D, sh, out, status, s)
+               : run_gather<int32_t>(vec, realign, *t, idx, n, D, sh, out, status, s);
+}
+}  // namespace
+}  // namespace dgs
+
+extern "C" int dgs_gather_rows(const dgs_chunk_desc* t, int32_t location_class, const void* idx,
+                               int32_t ids64, int64_t n, int64_t D, void* out, int32_t* status,
+                               dgs_stream_t stream) {
+  (void)location_class;  // hint only: the owner is resolved per row for every class
+  return dgs::gather_entry("dgs_gather_rows", t, idx, ids64, dgs::exact_count(n), D, out, status, stream);
+}
+
+extern "C" int dgs_gather_rows_counted(const dgs_chunk_desc* t, const void* idx, int32_t ids64, int64_t n_bound,
+                                       const int64_t* n_dev, int64_t D, void* out, int32_t* status,
+                                       dgs_stream_t stream) {
+  using namespace dgs;
+  DGS_REQUIRE(n_dev != nullptr, DGS_ERR_INVALID, "dgs_gather_rows_counted: null row count");
+  return gather_entry("dgs_gather_rows_counted", t, idx, ids64, Count{n_bound, n_dev, nullptr}, D, out, status, stream);
 }
 
 extern "C" int64_t dgs_cache_table_slots(int64_t n_keys) {

@@ -198,7 +198,7 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
                       const Count nc, const int64_t k, const bool replace,
                       const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
                       const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
-                      const uint32_t* __restrict__ order, const uint64_t key, IdT* coo_row, IdT* coo_col,
+                      const uint64_t key, IdT* coo_row, IdT* coo_col,
                       const int64_t out_capacity, int64_t* __restrict__ picked_pos,
                       const bool row_is_position, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
@@ -218,8 +218,7 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
     // everything that only needs the slot is read before the live count arrives (all arrays have room for
     // nc.bound entries); what belongs to a slot past the count is dropped below
     const bool in_bound = slot < nc.bound;
-    // which seed this group serves: the slot itself, or the slot's entry of the processing order
-    const int64_t i = (in_bound && order != nullptr) ? static_cast<int64_t>(order[slot]) : slot;
+    const int64_t i = slot;  // the seed this group serves
     const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, in_bound);
     const int64_t seed_raw = !in_bound ? 0 : (row_is_position ? i : static_cast<int64_t>(seeds[i]));
     const bool valid = slot < count_of(nc);
@@ -435,7 +434,7 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
                        const Count nc, const int64_t k, const bool replace,
                        const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
                        const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
-                       const uint32_t* __restrict__ order, const uint64_t key, IdT* coo_row, IdT* coo_col,
+                       const uint64_t key, IdT* coo_row, IdT* coo_col,
                        const int64_t out_capacity, int64_t* __restrict__ picked_pos,
                        const bool row_is_position, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
@@ -456,7 +455,7 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
   do {
     const int64_t slot = static_cast<int64_t>(blockIdx.x) * WARPS + warp;
     if (slot >= n) break;  // warp-uniform
-    const int64_t i = order != nullptr ? static_cast<int64_t>(order[slot]) : slot;
+    const int64_t i = slot;
     const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, true);
     const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
     const int64_t seed = row_is_position ? i : static_cast<int64_t>(seeds[i]);
@@ -538,8 +537,7 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
   __syncthreads();
   const int nhub = s_nhub;
   for (int h = 0; h < nhub; ++h) {
-    const int64_t slot = static_cast<int64_t>(blockIdx.x) * WARPS + s_hub[h];
-    const int64_t i = order != nullptr ? static_cast<int64_t>(order[slot]) : slot;
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * WARPS + s_hub[h];
     const SeedPlan sp = seed_plan(plan_rb, plan_deg, local_off, tile_off, i, true);
     const int64_t deg = sp.deg, rb = sp.rb, o = sp.o;
     const uint32_t i_lo = static_cast<uint32_t>(i), i_hi = static_cast<uint32_t>(static_cast<uint64_t>(i) >> 32);
@@ -588,13 +586,13 @@ int plan_typed(const dgs_chunk_desc& indptr, const void* seeds, Count n, int64_t
 
 template <typename IdT>
 int uniform_typed(const dgs_chunk_desc& indices, const void* seeds, Count n, int64_t k, bool replace,
-                  const PlanView& pv, const uint32_t* order, uint64_t key, void* coo_row, void* coo_col,
+                  const PlanView& pv, uint64_t key, void* coo_row, void* coo_col,
                   int64_t cap, int64_t* pos, bool rowpos, int32_t* status, cudaStream_t s) {
 #define DGS_LAUNCH_U(G)                                                                                      \
   DGS_CUDA_TRY(launch_chained(SITE_SAMPLE, sample_uniform_kernel<IdT, G>,                                                 \
                               static_cast<unsigned>((n.bound + SAMPLE_BLOCK / G - 1) / (SAMPLE_BLOCK / G)),  \
                               SAMPLE_BLOCK, s, indices, static_cast<const IdT*>(seeds), n, k, replace,       \
-                              pv.row_begin, pv.deg, pv.local_off, pv.tile_off, order, key,                   \
+                              pv.row_begin, pv.deg, pv.local_off, pv.tile_off, key,                          \
                               static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap, pos, rowpos, status))
   if (k <= 4) DGS_LAUNCH_U(4);
   else if (k <= 8) DGS_LAUNCH_U(8);
@@ -606,13 +604,13 @@ int uniform_typed(const dgs_chunk_desc& indices, const void* seeds, Count n, int
 
 template <typename IdT>
 int weighted_typed(const dgs_chunk_desc& indices, const dgs_chunk_desc& probs, const void* seeds, Count n,
-                   int64_t k, bool replace, const PlanView& pv, const uint32_t* order, uint64_t key,
+                   int64_t k, bool replace, const PlanView& pv, uint64_t key,
                    void* coo_row, void* coo_col, int64_t cap, int64_t* pos, bool rowpos, int32_t* status,
                    cudaStream_t s) {
   const unsigned grid = static_cast<unsigned>((n.bound + SAMPLE_BLOCK / 32 - 1) / (SAMPLE_BLOCK / 32));
   DGS_CUDA_TRY(launch_chained(SITE_SAMPLE, sample_weighted_kernel<IdT>, grid, SAMPLE_BLOCK, s, indices, probs,
                               static_cast<const IdT*>(seeds), n, k, replace, pv.row_begin, pv.deg, pv.local_off,
-                              pv.tile_off, order, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap,
+                              pv.tile_off, key, static_cast<IdT*>(coo_row), static_cast<IdT*>(coo_col), cap,
                               pos, rowpos, status));
   return DGS_OK;
 }
@@ -637,24 +635,24 @@ int launch_sample_plan(const dgs_chunk_desc& indptr, const void* seeds, bool ids
 }
 
 int launch_sample_uniform(const dgs_chunk_desc& indices, const void* seeds, bool ids64, Count n, int64_t k,
-                          bool replace, void* plan, const uint32_t* order, uint64_t key, void* coo_row,
+                          bool replace, void* plan, uint64_t key, void* coo_row,
                           void* coo_col, int64_t out_capacity, int64_t* picked_pos, bool row_is_position,
                           int32_t* status, cudaStream_t s) {
   const PlanView pv = plan_view(plan, n.bound);
-  return ids64 ? uniform_typed<int64_t>(indices, seeds, n, k, replace, pv, order, key, coo_row, coo_col,
+  return ids64 ? uniform_typed<int64_t>(indices, seeds, n, k, replace, pv, key, coo_row, coo_col,
                                         out_capacity, picked_pos, row_is_position, status, s)
-               : uniform_typed<int32_t>(indices, seeds, n, k, replace, pv, order, key, coo_row, coo_col,
+               : uniform_typed<int32_t>(indices, seeds, n, k, replace, pv, key, coo_row, coo_col,
                                         out_capacity, picked_pos, row_is_position, status, s);
 }
 
 int launch_sample_weighted(const dgs_chunk_desc& indices, const dgs_chunk_desc& probs, const void* seeds,
-                           bool ids64, Count n, int64_t k, bool replace, void* plan, const uint32_t* order,
+                           bool ids64, Count n, int64_t k, bool replace, void* plan,
                            uint64_t key, void* coo_row, void* coo_col, int64_t out_capacity,
                            int64_t* picked_pos, bool row_is_position, int32_t* status, cudaStream_t s) {
   const PlanView pv = plan_view(plan, n.bound);
-  return ids64 ? weighted_typed<int64_t>(indices, probs, seeds, n, k, replace, pv, order, key, coo_row, coo_col,
+  return ids64 ? weighted_typed<int64_t>(indices, probs, seeds, n, k, replace, pv, key, coo_row, coo_col,
                                          out_capacity, picked_pos, row_is_position, status, s)
-               : weighted_typed<int32_t>(indices, probs, seeds, n, k, replace, pv, order, key, coo_row, coo_col,
+               : weighted_typed<int32_t>(indices, probs, seeds, n, k, replace, pv, key, coo_row, coo_col,
                                          out_capacity, picked_pos, row_is_position, status, s);
 }
 
@@ -690,7 +688,7 @@ extern "C" int dgs_sample_plan(const dgs_chunk_desc* indptr, const void* seeds, 
 
 extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* seeds, int32_t ids64,
                                   int64_t n, int64_t k, int32_t replace, const void* plan,
-                                  const uint32_t* order, uint64_t rng_seed, uint64_t rng_offset,
+                                  uint64_t rng_seed, uint64_t rng_offset,
                                   void* coo_row, void* coo_col, int64_t out_capacity, int64_t* nnz,
                                   int64_t* picked_pos, int32_t* status, dgs_stream_t stream) {
   using namespace dgs;
@@ -711,7 +709,7 @@ extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* see
   DGS_REQUIRE(out_capacity == 0 || (coo_row != nullptr && coo_col != nullptr), DGS_ERR_INVALID,
               "dgs_sample_uniform: null output");
   rc = launch_sample_uniform(*indices, seeds, ids64 != 0, exact_count(n), k, replace != 0, const_cast<void*>(plan),
-                             order, sample_rng_key(rng_seed, rng_offset), coo_row, coo_col, out_capacity,
+                             sample_rng_key(rng_seed, rng_offset), coo_row, coo_col, out_capacity,
                              picked_pos, false, status, s);
   if (rc != DGS_OK) return rc;
   if (nnz != nullptr) {
@@ -723,7 +721,7 @@ extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* see
 
 extern "C" int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chunk_desc* probs,
                                    const void* seeds, int32_t ids64, int64_t n, int64_t k,
-                                   int32_t replace, const void* plan, const uint32_t* order,
+                                   int32_t replace, const void* plan,
                                    uint64_t rng_seed, uint64_t rng_offset, void* coo_row, void* coo_col,
                                    int64_t out_capacity, int64_t* nnz, int64_t* picked_pos,
                                    int32_t* status, dgs_stream_t stream) {
@@ -751,7 +749,7 @@ extern "C" int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chun
   DGS_REQUIRE(out_capacity == 0 || (coo_row != nullptr && coo_col != nullptr), DGS_ERR_INVALID,
               "dgs_sample_weighted: null output");
   rc = launch_sample_weighted(*indices, *probs, seeds, ids64 != 0, exact_count(n), k, replace != 0,
-                              const_cast<void*>(plan), order, sample_rng_key(rng_seed, rng_offset), coo_row,
+                              const_cast<void*>(plan), sample_rng_key(rng_seed, rng_offset), coo_row,
                               coo_col, out_capacity, picked_pos, false, status, s);
   if (rc != DGS_OK) return rc;
   if (nnz != nullptr) {

@@ -128,21 +128,6 @@ DGS_API int64_t dgs_alloc_current_bytes(void);
  * word (replaces the device asserts of src/cuda/*.cu).  `status` arguments
  * below are device-writable int32 words (pinned memory is fine) or NULL. */
 
-/* ---- locality order ------------------------------------------------------ */
-/* No counterpart in the reference.  order[0..n) becomes a permutation of
- * 0..n-1 that lists the request's positions in coarse address order (counting
- * sort on the high bits of the id; id_space = number of rows / nodes).  Passing
- * it to dgs_gather_rows / dgs_sample_* makes them visit the ids in that order
- * while writing every result where it belongs in the request: same output,
- * far fewer distinct pages in flight.  Optional: it helps when address
- * translation limits a request (mappings on small pages), and costs a few
- * percent when it does not.
- * scratch: dgs_locality_order_scratch_bytes() bytes. */
-DGS_API size_t dgs_locality_order_scratch_bytes(void);
-DGS_API int dgs_locality_order(const void* ids, int32_t ids64, int64_t n, int64_t id_space,
-                               uint32_t* order, void* scratch, size_t scratch_bytes,
-                               dgs_stream_t stream);
-
 /* ---- row gather -------------------------------------------------------- */
 enum { DGS_CLASS_ANY = 0, DGS_CLASS_LOCAL = 1, DGS_CLASS_REMOTE = 2, DGS_CLASS_HOST = 3 };
 /* IndexFromChunkTensorCUDA / Local.. / Remote.. / Host..,
@@ -150,11 +135,23 @@ enum { DGS_CLASS_ANY = 0, DGS_CLASS_LOCAL = 1, DGS_CLASS_REMOTE = 2, DGS_CLASS_H
  *   out[i*D + j] = T.At(idx[i]*D + j),  i < n, j < D.
  * `location_class` is a hint only (all classes resolve the owner per row, so
  * the result is the same for ids of any class).  A row id outside the tensor
- * yields a zero row and DGS_ERR_RANGE in *status.  `order` is NULL or a
- * permutation from dgs_locality_order(idx, ...): processing order only. */
+ * yields a zero row and DGS_ERR_RANGE in *status. */
 DGS_API int dgs_gather_rows(const dgs_chunk_desc* t, int32_t location_class,
                     const void* idx, int32_t ids64, int64_t n, int64_t D,
-                    void* out, const uint32_t* order, int32_t* status, dgs_stream_t stream);
+                    void* out, int32_t* status, dgs_stream_t stream);
+
+/* dgs_gather_rows for a request whose length is only known on the device: the
+ * kernel gathers min(*n_dev, n_bound) rows, n_dev being a device word that an
+ * earlier kernel on the same stream writes (e.g. the frontier length of
+ * dgs_sample_blocks, see dgs_sample_blocks_frontier_count); the host sizes
+ * `out` for n_bound rows.  This lets the feature gather of a mini-batch
+ * (features._CAPI_index(input_nodes) in the reference's training loop,
+ * oppo_bench/single_node/chunktensor.py:147-150) be queued directly behind the
+ * sampling sequence, without the host reading the frontier length first.
+ * No counterpart in the reference, which reads every size back. */
+DGS_API int dgs_gather_rows_counted(const dgs_chunk_desc* t, const void* idx, int32_t ids64,
+                                    int64_t n_bound, const int64_t* n_dev, int64_t D,
+                                    void* out, int32_t* status, dgs_stream_t stream);
 
 /* SplitIndexFromChunkTensorCUDA, src/cuda/index_with_chunk_tensor.cu:55-108.
  * Stable 3-way partition of the ids: out = [local ids | remote ids | host ids]
@@ -214,11 +211,10 @@ DGS_API int dgs_sample_plan(const dgs_chunk_desc* indptr, const void* seeds, int
  * If picked_pos != NULL it receives, per output, the position inside the row
  * (int64) -- a test hook for multigraph validity checks.
  * Randomness: Philox4x32-10 keyed by `rng_seed`, counter from `rng_offset`
- * and the seed position; identical arguments give identical output.
- * `order` is NULL or a permutation from dgs_locality_order(seeds, ...). */
+ * and the seed position; identical arguments give identical output. */
 DGS_API int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* seeds,
                        int32_t ids64, int64_t n_seeds, int64_t k, int32_t replace,
-                       const void* plan, const uint32_t* order, uint64_t rng_seed, uint64_t rng_offset,
+                       const void* plan, uint64_t rng_seed, uint64_t rng_offset,
                        void* coo_row, void* coo_col, int64_t out_capacity,
                        int64_t* nnz, int64_t* picked_pos, int32_t* status,
                        dgs_stream_t stream);
@@ -231,7 +227,7 @@ DGS_API int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* seeds,
  * With replacement: k draws proportional to max(w,0). */
 DGS_API int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chunk_desc* probs,
                         const void* seeds, int32_t ids64, int64_t n_seeds,
-                        int64_t k, int32_t replace, const void* plan, const uint32_t* order,
+                        int64_t k, int32_t replace, const void* plan,
                         uint64_t rng_seed, uint64_t rng_offset, void* coo_row,
                         void* coo_col, int64_t out_capacity, int64_t* nnz,
                         int64_t* picked_pos, int32_t* status, dgs_stream_t stream);
@@ -311,6 +307,13 @@ DGS_API int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_desc
                               uint64_t rng_seed, uint64_t rng_offset, void* workspace,
                               size_t workspace_bytes, int64_t* sizes, int32_t* status,
                               dgs_stream_t stream);
+
+/* Device address (inside `workspace`) of the word that holds the length of the
+ * last hop's frontier once the sequence queued by dgs_sample_blocks with the same
+ * hops / workspace has run: the n_dev of dgs_gather_rows_counted.  NULL on bad
+ * arguments.  No counterpart in the reference. */
+DGS_API const int64_t* dgs_sample_blocks_frontier_count(const dgs_hop* hops, int32_t n_hops,
+                                                        void* workspace);
 
 /* ---- PaGraph-style feature cache ---------------------------------------- */
 /* CreateHashMapTensorCUDA, src/cuda/pagraph.cu:94-124: open-addressing table

@@ -10,8 +10,13 @@
 #   2. const_cast in _getTensorVoidDataPtr (storage().data() is const void* now);
 #   3. `&cuda::X` -> `&dgs::cuda::X` in pybind.cc (ambiguous with libcu++'s ::cuda).
 # Its own build system (cmake) is not used.  Needs libtorch and NCCL headers; ~2 min per file.
+# Usage: build_reference.sh <checkout of gpzlx1/Dist-GPU-sampling>   (or DGS_REFERENCE_DIR in the environment)
 set -e
-REF=${1:-/root/reference}
+REF=${1:-$DGS_REFERENCE_DIR}
+if [ -z "$REF" ] || [ ! -d "$REF/src/cuda" ]; then
+  echo "usage: $0 <reference checkout> (no src/cuda under '$REF')" >&2
+  exit 2
+fi
 HERE=$(cd "$(dirname "$0")" && pwd)
 OUT=$HERE/_ref
 WORK=$(mktemp -d /tmp/dgs_ref_build.XXXXXX)

@@ -39,6 +39,16 @@ int dgs_oracle_num_threads(void) {
 #endif
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1 to their children; the timed CPU baseline asks
+ * for the host's cores explicitly instead of inheriting that. */
+void dgs_oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------------
  * Placement: src/chunk_tensor.cc:53-73.
  *   each = cap / esz; thr = each * W; if thr > total { thr = total;

@@ -46,6 +46,17 @@ def num_threads():
     return int(lib().dgs_oracle_num_threads())
 
 
+def use_all_cores():
+    """OpenMP threads = the cores this process may run on, whatever OMP_NUM_THREADS the launcher exported
+    (torchrun sets it to 1 for its children).  Returns the thread count now in use."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().dgs_oracle_set_num_threads(ctypes.c_int(max(1, n)))
+    return num_threads()
+
+
 def _p(a):
     return a.ctypes.data_as(ctypes.c_void_p)
 

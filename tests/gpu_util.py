@@ -71,28 +71,16 @@ class EmulatedChunks:
         self.desc = d
 
 
-def locality_order(ids_t, id_space):
-    """dgs_locality_order -> int32 tensor holding the uint32 permutation."""
-    abi = pkg.load_abi()
-    n = ids_t.numel()
-    order = torch.full((max(n, 1),), -1, dtype=torch.int32, device="cuda")
-    sb = abi.dgs_locality_order_scratch_bytes()
-    scratch = torch.empty(sb, dtype=torch.uint8, device="cuda")
-    pkg.check(abi.dgs_locality_order(vp(ids_t), int(ids_t.dtype == torch.int64), n, id_space, vp(order),
-                                     vp(scratch), sb, None))
-    return order[:n]
-
-
-def gather(desc, idx_t, D, dtype, words, cls=0, order=None):
+def gather(desc, idx_t, D, dtype, words, cls=0):
     abi = pkg.load_abi()
     n = idx_t.numel()
     out = torch.empty((n, D), dtype=dtype, device="cuda")
     pkg.check(abi.dgs_gather_rows(ctypes.byref(desc), cls, vp(idx_t), int(idx_t.dtype == torch.int64), n, D,
-                                  vp(out), vp(order), vp(words.status), None))
+                                  vp(out), vp(words.status), None))
     return out
 
 
-def sample(indptr_desc, indices_desc, seeds_t, k, replace, words, probs_desc=None, rng=(1, 0), order=None):
+def sample(indptr_desc, indices_desc, seeds_t, k, replace, words, probs_desc=None, rng=(1, 0)):
     """plan + sample through the C ABI; returns (row, col, pos) as numpy."""
     abi = pkg.load_abi()
     n = seeds_t.numel()
@@ -106,11 +94,11 @@ def sample(indptr_desc, indices_desc, seeds_t, k, replace, words, probs_desc=Non
                                   None, vp(words.status), None))
     if probs_desc is None:
         pkg.check(abi.dgs_sample_uniform(ctypes.byref(indices_desc), vp(seeds_t), ids64, n, k, int(replace),
-                                         vp(plan), vp(order), rng[0], rng[1], vp(row), vp(col), n * k,
+                                         vp(plan), rng[0], rng[1], vp(row), vp(col), n * k,
                                          vp(words.sizes), vp(pos), vp(words.status), None))
     else:
         pkg.check(abi.dgs_sample_weighted(ctypes.byref(indices_desc), ctypes.byref(probs_desc), vp(seeds_t),
-                                          ids64, n, k, int(replace), vp(plan), vp(order), rng[0], rng[1],
+                                          ids64, n, k, int(replace), vp(plan), rng[0], rng[1],
                                           vp(row), vp(col), n * k, vp(words.sizes), vp(pos), vp(words.status),
                                           None))
     torch.cuda.synchronize()

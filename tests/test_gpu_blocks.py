@@ -219,3 +219,54 @@ def test_blocks_through_the_c_abi(oracle, pkg):
     assert nnz0 + nnz1 == check_hops(oracle, indptr, indices, seeds, fanouts, False, bufs[1][2][:nu1], blocks)
     # nothing is written past the reported sizes
     assert bool((bufs[0][0][nnz0:] == -7).all()) and bool((bufs[1][2][nu1:] == -7).all())
+
+
+@pytest.mark.parametrize("weighted", [False, True])
+def test_blocks_over_emulated_multi_gpu_chunks(oracle, pkg, weighted):
+    """dgs_sample_blocks through the C ABI over indptr / indices / weights split into four device parts plus a
+    host tail, with chunk boundaries that fall at odd element offsets -- the layout of a multi-GPU run."""
+    from gpu_util import EmulatedChunks, vp
+    abi = pkg.load_abi()
+    rng = np.random.default_rng(17)
+    indptr, indices = graph(rng, 9000, 30, hubs=(0, 700))
+    probs = (rng.random(indices.size) + 0.05).astype(np.float32)
+    e_ip = EmulatedChunks(indptr, 1, 8 * 1801, 4, rank=2)                 # 4 x 1801 elements, rest on the host
+    e_ix = EmulatedChunks(indices, 1, 8 * (indices.size // 5 + 3), 4, rank=1)
+    e_pr = EmulatedChunks(probs, 1, 4 * (indices.size // 5 + 3), 4, rank=1)
+    assert e_ip.host_n > 0 and e_ix.host_n > 0
+    seeds = rng.permutation(9000)[:400]
+    seeds[:2] = [0, 1]
+    sd = to_dev(seeds)
+    for fanouts in ([5, 10], [31, 32]):                                   # stochastic rows / (almost) whole rows
+        H = len(fanouts)
+        applied = (ctypes.c_int64 * H)(*reversed(fanouts))
+        hops = (pkg.Hop * H)()
+        pkg.check(abi.dgs_sample_blocks_bounds(seeds.size, applied, H, 9000, hops))
+        wsb = abi.dgs_sample_blocks_workspace_bytes(hops, H)
+        ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+        bufs = []
+        for h in range(H):
+            cap = hops[h].seed_bound * hops[h].fanout
+            r, c = torch.full((cap,), -7, device="cuda"), torch.full((cap,), -7, device="cuda")
+            fr = torch.full((hops[h].frontier_bound,), -7, device="cuda")
+            hops[h].coo_row, hops[h].coo_col, hops[h].frontier = vp(r), vp(c), vp(fr)
+            bufs.append((r, c, fr))
+        sizes = torch.zeros(2 * H, dtype=torch.int64).pin_memory()
+        status = torch.zeros(1, dtype=torch.int32).pin_memory()
+        pkg.check(abi.dgs_sample_blocks(ctypes.byref(e_ip.desc), ctypes.byref(e_ix.desc),
+                                        ctypes.byref(e_pr.desc) if weighted else None, vp(sd), 1, hops, H, 0, 11, 0,
+                                        vp(ws), wsb, vp(sizes), vp(status), None))
+        # the frontier length is also where dgs_sample_blocks_frontier_count says it is
+        n_dev = abi.dgs_sample_blocks_frontier_count(hops, H, vp(ws))
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        sz = sizes.tolist()
+        assert ws.data_ptr() <= n_dev < ws.data_ptr() + wsb
+        word = ws[n_dev - ws.data_ptr(): n_dev - ws.data_ptr() + 8].view(torch.int64).item()
+        assert word == sz[2 * H - 1]
+        blocks, n_dst = [], seeds.size
+        for h in range(H):
+            blocks.insert(0, (bufs[h][0][:sz[2 * h]], bufs[h][1][:sz[2 * h]], sz[2 * h + 1], n_dst))
+            n_dst = sz[2 * h + 1]
+        total = check_hops(oracle, indptr, indices, seeds, fanouts, False, bufs[H - 1][2][:n_dst], blocks)
+        assert total == sum(sz[0::2])

@@ -59,30 +59,30 @@ def test_gather_matches_oracle(oracle, words, rows, D, dtype, cap_elems, world, 
 
 
 @pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
-def test_locality_order_changes_nothing_but_the_visiting_order(oracle, words, idx_dtype):
-    """A processing order from dgs_locality_order is a permutation sorted by coarse
-    address, and gathering with it gives the same bytes as without."""
-    from gpu_util import EmulatedChunks, gather, locality_order
+def test_gather_with_a_device_side_row_count(pkg, words, idx_dtype):
+    """dgs_gather_rows_counted: the request length is a device word (as the frontier length of a queued
+    sample_blocks sequence is); rows up to min(word, bound) are gathered, nothing is written past them."""
+    import ctypes
+    from gpu_util import EmulatedChunks, vp
+    abi = pkg.load_abi()
     rng = np.random.default_rng(12)
     rows, D = 300_000, 100
     table = rng.standard_normal((rows, D)).astype(np.float32)
     em = EmulatedChunks(table, D, 4 * (D * 70_000 + 36), 4)       # 4 chunks + host tail, straddling rows
     idx = rng.integers(0, rows, size=200_001)
-    idx[5] = rows + 3                                               # one bad id: still a zero row
     idx_t = torch.from_numpy(idx).to(idx_dtype).cuda()
-    order = locality_order(idx_t, rows)
-    o = order.cpu().numpy().astype(np.int64) & 0xFFFFFFFF
-    assert np.array_equal(np.sort(o), np.arange(idx.size))          # a permutation
-    bins = np.clip(idx[o], 0, None) >> max(0, int(np.ceil(np.log2(rows))) - 12)
-    assert (np.diff(np.minimum(bins, 4095)) >= 0).all()             # coarse address order
-    plain = gather(em.desc, idx_t, D, torch.float32, words)
-    assert words.take_status() == 6
-    ordered = gather(em.desc, idx_t, D, torch.float32, words, order=order)
-    assert words.take_status() == 6
-    assert torch.equal(plain, ordered)
-    good = np.delete(np.arange(idx.size), 5)
-    assert ordered.cpu().numpy()[good].tobytes() == table[idx[good]].tobytes()
-    assert locality_order(idx_t[:0], rows).numel() == 0
+    for live, bound in ((150_003, 200_001), (0, 200_001), (200_001, 200_001), (10 ** 9, 70_000), (-5, 1000)):
+        n_dev = torch.tensor([live], dtype=torch.int64, device="cuda")
+        out = torch.full((bound, D), -7.0, dtype=torch.float32, device="cuda")
+        pkg.check(abi.dgs_gather_rows_counted(ctypes.byref(em.desc), vp(idx_t), int(idx_dtype == torch.int64), bound,
+                                              vp(n_dev), D, vp(out), vp(words.status), None))
+        assert words.take_status() == 0
+        n = max(0, min(live, bound))
+        got = out.cpu().numpy()
+        assert got[:n].tobytes() == table[idx[:n]].tobytes()
+        assert (got[n:] == -7.0).all()
+    rc = abi.dgs_gather_rows_counted(ctypes.byref(em.desc), vp(idx_t), 1, 10, None, D, vp(out), None, None)
+    assert rc == 1 and b"row count" in abi.dgs_last_error()
 
 
 def test_gather_empty_and_out_of_range(words):

@@ -52,26 +52,6 @@ def test_uniform_validity(oracle, words, k, replace, idt):
         assert not np.array_equal(pos, pos3)
 
 
-@pytest.mark.parametrize("weighted", [False, True])
-def test_processing_order_does_not_change_the_sample(words, weighted):
-    """Randomness is keyed by the seed's position in the request, not by the order
-    in which seeds are visited: with a locality order the output is identical."""
-    from gpu_util import plain_desc, sample, locality_order
-    rng = np.random.default_rng(55)
-    indptr, indices = small_graph(rng)
-    probs = torch.from_numpy(rng.random(indices.size).astype(np.float32) + 0.01).cuda()
-    seeds = rng.integers(0, 300, size=5000)
-    ip, ix, sd = to_dev(indptr), to_dev(indices), to_dev(seeds)
-    order = locality_order(sd, 300)
-    pd = plain_desc(probs) if weighted else None
-    for k, replace in [(10, False), (6, True), (40, False) if not weighted else (32, False)]:
-        a = sample(plain_desc(ip), plain_desc(ix), sd, k, replace, words, probs_desc=pd, rng=(9, k))
-        b = sample(plain_desc(ip), plain_desc(ix), sd, k, replace, words, probs_desc=pd, rng=(9, k), order=order)
-        assert words.take_status() == 0
-        for x, y in zip(a, b):
-            assert np.array_equal(x, y)
-
-
 def test_full_rows_golden(words):
     """deg <= k everywhere: the output is the frozen oracle output, bit for bit."""
     from gpu_util import plain_desc, sample
