@@ -259,10 +259,11 @@ class PipelinedSampler:
         for input_nodes, blocks, n_edges, x in sampler(seed_batches):
             ...   # blocks = [(coo_row, coo_col, n_src, n_dst)] in layer order, x = features[input_nodes]
 
-    `depth` batches are sampled (and their features gathered) ahead of the one being consumed, each on a
-    stream of its own, so the small hops of one batch overlap with the gather of another.  What a batch
-    yields are views into its slot: valid until `depth` - 1 further batches have been drawn from the
-    iterator; clone what must live longer.  indptr / indices / probs / features are ChunkTensors; seed
+    Up to `depth` batches are in flight, each on a stream of its own, so the small hops of one batch overlap
+    with the gather of another and with the consumer of the batch before.  What a batch yields are views into
+    its slot: valid until the NEXT batch is drawn from the iterator (that is when the slot is handed to a new
+    batch); clone what must live longer.  With submit() / next() called by hand, a batch stays valid until
+    the submit() that reuses its slot, the depth-th after its own.  indptr / indices / probs / features are ChunkTensors; seed
     batches are tensors on the GPU or in (pinned) host memory, at most max_seeds ids each.  Results follow
     the same rules as sample_blocks(): identical wherever no random choice is involved.
     Delete the sampler before the ChunkTensors it reads (their destructor is collective).
@@ -314,3 +315,8 @@ def block_csc(coo_row, coo_col, n_dst, rows_sorted=True):
     if coo_row.numel():
         indptr[1:] = torch.cumsum(torch.bincount(coo_row.to(torch.int64), minlength=n_dst)[:n_dst], 0)
     return indptr, coo_col
+
+
+# placement policy (capacity planning in the reference's priority order, free-memory rule, renumbering by degree)
+from .placement import (CACHE_PRIORITY, get_available_memory, permute_edge_tensor, plan_capacities,  # noqa: E402,F401
+                        reduce_min_over_ranks, renumber_by_degree)

@@ -17,10 +17,11 @@
 // kernels of one batch's small hops run while another batch's gather keeps the
 // memory system (HBM, NVLink, host link) busy.
 //
-// Lifetime of the results: views into the slot, valid until the slot is submitted
-// to again, i.e. for `depth` - 1 further submit() calls.  A submit() first makes
-// the slot's stream wait for everything queued so far on the caller's current
-// stream, so consumers that were launched there before that submit() are safe.
+// Lifetime of the results: views into the slot, valid until the submit() that
+// takes the slot again (the depth-th submit() after the one that queued the
+// batch).  That submit() first makes the slot's stream wait for everything queued
+// so far on the caller's current stream, so consumers that were launched there
+// before it are safe.
 //
 // No counterpart in src/pybind.cc: an addition like the _CAPI_sample_blocks*
 // operators, built from the same C ABI calls.
@@ -89,10 +90,23 @@ class BlockPipeline : public torch::CustomClassHolder {
     const auto dev = torch::Device(torch::kCUDA, static_cast<c10::DeviceIndex>(device_));
     const auto id_opt = torch::TensorOptions().dtype(indptr_->dtype()).device(dev);
     slots_.resize(depth);
+    // The sampling sequence is a chain of short, latency-bound kernels; the feature gather is one long
+    // bandwidth-bound kernel whose CTAs would otherwise queue up in front of every other batch's sampling
+    // kernels.  So each slot samples on a high-priority stream and gathers on a low-priority one: whenever an
+    // SM has room, CTAs of some batch's sampling kernels are placed first and the gather fills the rest.
+    int prio_low = 0, prio_high = 0;
+    TORCH_CHECK(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high) == cudaSuccess,
+                "BlockPipeline: cannot query stream priorities");
+    static const char* one_stream = std::getenv("DGS_PIPELINE_ONE_STREAM");  // measurement switch
+    const bool split = features_.defined() && !(one_stream != nullptr && one_stream[0] == '1');
     for (Slot& s : slots_) {
-      TORCH_CHECK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess,
+      TORCH_CHECK(cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, split ? prio_high : prio_low) == cudaSuccess,
                   "BlockPipeline: cannot create a stream");
+      if (split)
+        TORCH_CHECK(cudaStreamCreateWithPriority(&s.gather_stream, cudaStreamNonBlocking, prio_low) == cudaSuccess,
+                    "BlockPipeline: cannot create a stream");
       TORCH_CHECK(cudaEventCreateWithFlags(&s.ready, cudaEventDisableTiming) == cudaSuccess &&
+                      cudaEventCreateWithFlags(&s.sampled, cudaEventDisableTiming) == cudaSuccess &&
                       cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming) == cudaSuccess,
                   "BlockPipeline: cannot create an event");
       void* p = nullptr;
@@ -120,9 +134,12 @@ class BlockPipeline : public torch::CustomClassHolder {
   ~BlockPipeline() override {
     for (Slot& s : slots_) {
       if (s.stream != nullptr) cudaStreamSynchronize(s.stream);
+      if (s.gather_stream != nullptr) cudaStreamSynchronize(s.gather_stream);
       if (s.ready != nullptr) cudaEventDestroy(s.ready);
+      if (s.sampled != nullptr) cudaEventDestroy(s.sampled);
       if (s.done != nullptr) cudaEventDestroy(s.done);
       if (s.stream != nullptr) cudaStreamDestroy(s.stream);
+      if (s.gather_stream != nullptr) cudaStreamDestroy(s.gather_stream);
       if (s.sizes != nullptr) cudaFreeHost(s.sizes);
     }
   }
@@ -169,14 +186,21 @@ class BlockPipeline : public torch::CustomClassHolder {
       DGS_CHECK_RC(dgs_sample_blocks(&indptr_->desc(), &indices_->desc(), probs_.defined() ? &probs_->desc() : nullptr,
                                      s.seeds.data_ptr(), ids64_, hops, H_, replace_, rng.first, rng.second,
                                      s.ws.data_ptr(), ws_bytes_, s.sizes, s.status, s.stream));
+      cudaStream_t last = s.stream;
       if (features_.defined()) {
         const int64_t* n_dev = dgs_sample_blocks_frontier_count(hops, H_, s.ws.data_ptr());
         TORCH_CHECK(n_dev != nullptr, "BlockPipeline.submit: no frontier count");
+        if (s.gather_stream != nullptr) {
+          TORCH_CHECK(cudaEventRecord(s.sampled, s.stream) == cudaSuccess &&
+                          cudaStreamWaitEvent(s.gather_stream, s.sampled, 0) == cudaSuccess,
+                      "BlockPipeline.submit: cannot order the gather after the sampling sequence");
+          last = s.gather_stream;
+        }
         DGS_CHECK_RC(dgs_gather_rows_counted(&features_->desc(), s.frontier[H_ - 1].data_ptr(), ids64_,
                                              s.frontier_bound[H_ - 1], n_dev, features_->elem_stride(),
-                                             s.feats.data_ptr(), s.status, s.stream));
+                                             s.feats.data_ptr(), s.status, last));
       }
-      TORCH_CHECK(cudaEventRecord(s.done, s.stream) == cudaSuccess, "BlockPipeline.submit: cannot record an event");
+      TORCH_CHECK(cudaEventRecord(s.done, last) == cudaSuccess, "BlockPipeline.submit: cannot record an event");
     }
     ++head_;
     ++in_flight_;
@@ -241,8 +265,9 @@ class BlockPipeline : public torch::CustomClassHolder {
   static constexpr int64_t kBudgetBytes = int64_t(32) << 30;
 
   struct Slot {
-    cudaStream_t stream = nullptr;
-    cudaEvent_t ready = nullptr, done = nullptr;
+    cudaStream_t stream = nullptr;         // sampling sequence (high priority when there is a gather stream)
+    cudaStream_t gather_stream = nullptr;  // feature gather (low priority); null: everything on `stream`
+    cudaEvent_t ready = nullptr, sampled = nullptr, done = nullptr;
     int64_t* sizes = nullptr;   // [2 * DGS_MAX_HOPS], pinned
     int32_t* status = nullptr;  // pinned
     torch::Tensor seeds, ws, feats;

@@ -325,6 +325,237 @@ int launch_gather_r(const Src& rows, Count nc, int64_t D, int sh, void* out, int
   return DGS_OK;
 }
 
+
+// ---- rows moved by the copy engine ------------------------------------------------
+// The kernel above keeps its bytes in flight in registers (eight 16-byte loads per thread), which at four
+// CTAs per SM is the whole register file: nothing else can run beside it.  This variant moves whole rows
+// with bulk asynchronous copies instead -- one cp.async.bulk per row from wherever the row lives (local HBM,
+// a peer's HBM over NVLink, pinned host memory) into shared memory, completion counted by an mbarrier, then
+// ONE bulk store per group of rows, because a group's output rows are contiguous.  The bytes in flight sit in
+// shared memory, a warp needs a handful of registers, and one small persistent CTA per SM is enough -- so the
+// short latency-bound kernels of other mini-batches' sampling sequences run on the same SMs at the same time.
+//
+// Every warp is its own pipeline (no CTA-wide barrier): STAGES buffers of `group` rows each; lane l owns row
+// l of the group.  Per group: resolve the row (as above), lane 0 announces the bytes to expect, every lane
+// issues its row's copy; rows that cannot be copied whole (they straddle two storage regions, or the id is
+// out of range) are written into the buffer by their lane with ordinary stores.  When the group has landed,
+// lane 0 issues the store, and the buffer is loaded again only after that store has read it
+// (cp.async.bulk.wait_group.read).  Needs rows that start on 16-byte boundaries and are a multiple of 16 bytes.
+// Waits are bounded: a copy that never completes sets DGS_ERR_CUDA in the status word and the warp leaves
+// after its outstanding stores.
+constexpr int BULK_WARPS = 4;
+constexpr int BULK_STAGES = 3;
+constexpr uint32_t BULK_WAIT_LIMIT = 1u << 24;  // polls of ~20 ns each: a fraction of a second
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  for (uint32_t polls = 0; polls < BULK_WAIT_LIMIT; ++polls)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// global -> shared, `bytes` a multiple of 16, both addresses 16-byte aligned; no multicast
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <typename Src>
+__global__ void __launch_bounds__(BULK_WARPS * 32)
+gather_rows_bulk_kernel(const __grid_constant__ Src rows, const int64_t n_bound, const int64_t* __restrict__ n_dev,
+                        const int64_t D, const int sh, const uint32_t row_bytes, const uint32_t group,
+                        const uint32_t stage_bytes, char* __restrict__ out, int32_t* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  unsigned char* my_stages = bulk_smem + static_cast<size_t>(warp) * BULK_STAGES * stage_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem + static_cast<size_t>(BULK_WARPS) * BULK_STAGES * stage_bytes) +
+                   warp * BULK_STAGES;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < BULK_STAGES; ++s) mbar_init(smem_addr(bars + s), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  pdl_enter();
+
+  int64_t n = n_bound;
+  if (n_dev != nullptr) {
+    const int64_t live = *n_dev;
+    n = live < n_bound ? (live < 0 ? 0 : live) : n_bound;
+  }
+  const int64_t n_groups = (n + group - 1) / group;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * BULK_WARPS;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * BULK_WARPS + warp;
+
+  // loads of group g into stage st
+  auto issue = [&](int64_t g, int st) {
+    const int64_t i = g * group + lane;
+    const bool valid = lane < static_cast<int>(group) && i < n;
+    const char* src = valid ? rows.template locate<16, false>(i, status) : nullptr;
+    const bool whole = valid && reinterpret_cast<uintptr_t>(src) > 1;
+    const uint32_t bar = smem_addr(bars + st);
+    unsigned char* slot = my_stages + static_cast<size_t>(st) * stage_bytes + static_cast<size_t>(lane) * row_bytes;
+    const uint32_t expect = static_cast<uint32_t>(__popc(__ballot_sync(FULL_MASK, whole))) * row_bytes;
+    if (lane == 0) mbar_expect_tx(bar, expect);  // also the one arrival the barrier waits for
+    __syncwarp();
+    if (whole) {
+      bulk_load(smem_addr(slot), src, row_bytes, bar);
+    } else if (valid) {
+      // rare: zero row (bad id) or a row that straddles two storage regions, element by element
+      const int esz = 1 << sh;
+      if (src == DGS_ROW_ZERO) {
+        for (uint32_t b = 0; b < row_bytes; b += 16) *reinterpret_cast<uint4*>(slot + b) = make_uint4(0u, 0u, 0u, 0u);
+      } else {
+        for (int64_t j = 0; j < D; ++j) {
+          const char* p = rows.element(i, j);
+          unsigned char* q = slot + (j << sh);
+          switch (esz) {
+            case 8: *reinterpret_cast<uint64_t*>(q) = *reinterpret_cast<const uint64_t*>(p); break;
+            case 4: *reinterpret_cast<uint32_t*>(q) = *reinterpret_cast<const uint32_t*>(p); break;
+            case 2: *reinterpret_cast<uint16_t*>(q) = *reinterpret_cast<const uint16_t*>(p); break;
+            default: *q = static_cast<unsigned char>(*p); break;
+          }
+        }
+      }
+      fence_async_smem();  // these ordinary stores must be visible to the bulk store that reads the buffer
+    }
+  };
+
+  // prologue: STAGES - 1 groups ahead
+  int64_t g_issue = first;
+#pragma unroll
+  for (int s = 0; s < BULK_STAGES - 1; ++s) {
+    if (g_issue < n_groups) issue(g_issue, s);
+    g_issue += stride;
+  }
+  uint32_t phase_bits = 0;  // parity of each stage's barrier
+  int st = 0, st_issue = BULK_STAGES - 1;
+  bool alive = true;
+  for (int64_t g = first; g < n_groups && alive; g += stride) {
+    const uint32_t bar = smem_addr(bars + st);
+    if (!mbar_wait_bounded(bar, (phase_bits >> st) & 1u)) {
+      raise_status(status, DGS_ERR_CUDA);
+      alive = false;
+    }
+    alive = __all_sync(FULL_MASK, alive);
+    if (!alive) break;
+    __syncwarp();  // rows that lanes wrote into the buffer themselves are visible to lane 0's store
+    phase_bits ^= 1u << st;
+    if (lane == 0) {
+      const int64_t row0 = g * group;
+      const int64_t rows_here = n - row0 < static_cast<int64_t>(group) ? n - row0 : static_cast<int64_t>(group);
+      bulk_store(out + row0 * row_bytes, smem_addr(my_stages + static_cast<size_t>(st) * stage_bytes),
+                 static_cast<uint32_t>(rows_here) * row_bytes);
+      // the buffer that is loaded next was stored from one iteration ago: that store must have read it
+      bulk_wait_read<1>();
+    }
+    __syncwarp();
+    if (g_issue < n_groups) issue(g_issue, st_issue);
+    g_issue += stride;
+    st = st + 1 == BULK_STAGES ? 0 : st + 1;
+    st_issue = st_issue + 1 == BULK_STAGES ? 0 : st_issue + 1;
+  }
+  if (!alive) {
+    // give the copies still in flight a bounded chance to land before the buffers go away
+    for (int s = 0; s < BULK_STAGES; ++s) mbar_wait_bounded(smem_addr(bars + s), (phase_bits >> s) & 1u);
+  }
+  if (lane == 0) bulk_wait_all();  // shared memory must outlive the stores that read it
+}
+
+// rows a warp moves per group and the bytes of one buffer, for rows of row_bytes
+inline void bulk_geometry(int64_t row_bytes, uint32_t* group, uint32_t* stage_bytes) {
+  uint32_t g = static_cast<uint32_t>(8192 / row_bytes);
+  if (g > 32) g = 32;
+  if (g < 1) g = 1;
+  *group = g;
+  *stage_bytes = (g * static_cast<uint32_t>(row_bytes) + 127u) / 128u * 128u;
+}
+
+// DGS_GATHER_BULK: 0 = never, 1 = whenever the rows qualify, unset = the default of the call site
+inline int bulk_env() {
+  static const int v = [] {
+    const char* e = std::getenv("DGS_GATHER_BULK");
+    return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+  }();
+  return v;
+}
+
+template <typename Src>
+int launch_gather_bulk(const Src& rows, Count nc, int64_t D, int sh, void* out, int32_t* status, cudaStream_t stream) {
+  const int64_t row_bytes = D << sh;
+  uint32_t group, stage_bytes;
+  bulk_geometry(row_bytes, &group, &stage_bytes);
+  const size_t smem = static_cast<size_t>(BULK_WARPS) * BULK_STAGES * stage_bytes + BULK_WARPS * BULK_STAGES * sizeof(uint64_t);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    DGS_CUDA_TRY(cudaGetDevice(&dev));
+    DGS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  static const int per_sm = [] {
+    const char* e = std::getenv("DGS_GATHER_BULK_CTAS_PER_SM");
+    const int v = e != nullptr ? std::atoi(e) : 1;
+    return v >= 1 && v <= 4 ? v : 1;
+  }();
+  const int64_t groups = (nc.bound + group - 1) / group;
+  int64_t grid = (groups + BULK_WARPS - 1) / BULK_WARPS;
+  if (grid > static_cast<int64_t>(sms) * per_sm) grid = static_cast<int64_t>(sms) * per_sm;
+  auto kernel = gather_rows_bulk_kernel<Src>;
+  static bool smem_opted_in = false;  // per instantiation; the buffers never exceed 12 x 8 KB + the barriers
+  if (!smem_opted_in) {
+    DGS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 12 * 8320 + 128));
+    smem_opted_in = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(BULK_WARPS * 32, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launches_enabled(SITE_GATHER) ? 1 : 0;
+  DGS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, rows, nc.bound, nc.dev, D, sh, static_cast<uint32_t>(row_bytes), group,
+                                  stage_bytes, static_cast<char*>(out), status));
+  return DGS_OK;
+}
+
+inline bool bulk_rows_qualify(int vec, bool realign, int64_t row_bytes) {
+  return vec == 16 && !realign && (row_bytes % 16) == 0 && row_bytes >= 256 && row_bytes <= 8192;
+}
+
 // realign: some storage region starts rows off the vector boundary (see vector_copy_ok)
 template <typename Src, int VEC>
 int launch_gather(const Src& rows, bool realign, Count n, int64_t D, int sh, void* out, int32_t* status,
@@ -347,10 +578,14 @@ int dispatch_vec(int vec, bool realign, const Src& rows, Count n, int64_t D, int
   }
 }
 
+// prefer_bulk: what the call site wants when DGS_GATHER_BULK does not say
 template <typename IdxT>
 int run_gather(int vec, bool realign, const dgs_chunk_desc& d, const void* idx, Count n, int64_t D, int sh,
-               void* out, int32_t* status, cudaStream_t stream) {
+               void* out, int32_t* status, bool prefer_bulk, cudaStream_t stream) {
   ChunkRows<IdxT> rows{d, static_cast<const IdxT*>(idx), D, d.total / D, sh};
+  const int env = bulk_env();
+  if ((env == 1 || (env < 0 && prefer_bulk)) && bulk_rows_qualify(vec, realign, D << sh))
+    return launch_gather_bulk(rows, n, D, sh, out, status, stream);
   return dispatch_vec(vec, realign, rows, n, D, sh, out, status, stream);
 }
 
@@ -469,7 +704,7 @@ int gather_vec_bytes(const dgs_chunk_desc& d, int64_t D, const void* out, bool* 
 namespace dgs {
 namespace {
 int gather_entry(const char* who, const dgs_chunk_desc* t, const void* idx, int32_t ids64, Count n, int64_t D,
-                 void* out, int32_t* status, dgs_stream_t stream) {
+                 void* out, int32_t* status, bool prefer_bulk, dgs_stream_t stream) {
   int rc = validate_desc(t, who);
   if (rc != DGS_OK) return rc;
   DGS_REQUIRE(n.bound >= 0 && D >= 1, DGS_ERR_INVALID, "%s: n=%lld D=%lld", who, (long long)n.bound, (long long)D);
@@ -479,8 +714,8 @@ int gather_entry(const char* who, const dgs_chunk_desc* t, const void* idx, int3
   bool realign = false;
   const int vec = gather_vec_bytes(*t, D, out, &realign);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return ids64 ? run_gather<int64_t>(vec, realign, *t, idx, n, D, sh, out, status, s)
-               : run_gather<int32_t>(vec, realign, *t, idx, n, D, sh, out, status, s);
+  return ids64 ? run_gather<int64_t>(vec, realign, *t, idx, n, D, sh, out, status, prefer_bulk, s)
+               : run_gather<int32_t>(vec, realign, *t, idx, n, D, sh, out, status, prefer_bulk, s);
 }
 }  // namespace
 }  // namespace dgs
@@ -489,7 +724,7 @@ extern "C" int dgs_gather_rows(const dgs_chunk_desc* t, int32_t location_class, 
                                int32_t ids64, int64_t n, int64_t D, void* out, int32_t* status,
                                dgs_stream_t stream) {
   (void)location_class;  // hint only: the owner is resolved per row for every class
-  return dgs::gather_entry("dgs_gather_rows", t, idx, ids64, dgs::exact_count(n), D, out, status, stream);
+  return dgs::gather_entry("dgs_gather_rows", t, idx, ids64, dgs::exact_count(n), D, out, status, false, stream);
 }
 
 extern "C" int dgs_gather_rows_counted(const dgs_chunk_desc* t, const void* idx, int32_t ids64, int64_t n_bound,
@@ -497,7 +732,7 @@ extern "C" int dgs_gather_rows_counted(const dgs_chunk_desc* t, const void* idx,
                                        dgs_stream_t stream) {
   using namespace dgs;
   DGS_REQUIRE(n_dev != nullptr, DGS_ERR_INVALID, "dgs_gather_rows_counted: null row count");
-  return gather_entry("dgs_gather_rows_counted", t, idx, ids64, Count{n_bound, n_dev, nullptr}, D, out, status, stream);
+  return gather_entry("dgs_gather_rows_counted", t, idx, ids64, Count{n_bound, n_dev, nullptr}, D, out, status, false, stream);
 }
 
 extern "C" int64_t dgs_cache_table_slots(int64_t n_keys) {

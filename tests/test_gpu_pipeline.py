@@ -61,14 +61,19 @@ def test_pipeline_stochastic_batches_are_valid_and_results_outlive_later_submits
     sampler = pkg.PipelinedSampler(c_ip, c_ix, fanouts, features=c_ft, max_seeds=512, depth=depth)
     torch.manual_seed(7)
     held = []
-    for i, (f, blocks, ne, x) in enumerate(sampler(pinned)):
+    # by hand: a batch handed out by next() stays intact, whatever the other slots are running, until the
+    # submit() that takes its slot again (the depth-th after its own)
+    for i in range(depth):
+        sampler.submit(pinned[i])
+    for i in range(len(batches)):
+        f, blocks, ne, x = sampler.next()
         held.append((f, blocks, ne, x, f.clone(), x.clone()))
-        # a batch stays intact while up to depth - 1 later batches are drawn
-        if len(held) >= depth:
-            of, _, _, ox, fc, xc = held[-depth]
-            assert torch.equal(of, fc) and torch.equal(ox, xc)
         assert ne == check_hops(oracle, indptr, indices, batches[i], fanouts, False, f, blocks)
         assert x.cpu().numpy().tobytes() == feats[f.cpu().numpy()].tobytes()
+        torch.cuda.synchronize()                  # let the younger batches run to completion
+        assert torch.equal(f, held[-1][4]) and torch.equal(x, held[-1][5])
+        if i + depth < len(batches):
+            sampler.submit(pinned[i + depth])     # from here on batch i's views belong to batch i + depth
     # same torch seed -> same batches again; another seed -> other samples
     torch.manual_seed(7)
     again = [(f.clone(), ne) for f, _, ne, _ in sampler(pinned)]

@@ -52,6 +52,15 @@ WORKER = textwrap.dedent('''
     dist.all_gather_object(allb, mine_b)
     flat = sorted(sum(allb, []))
     assert flat == list(range(batches.shape[0]))
+    # free memory differs per rank: the group plans with the minimum, and every rank derives the same plan
+    avail = pkg.reduce_min_over_ranks(10 ** 9 + rank * 12345)
+    assert avail == 10 ** 9
+    graph = {"indptr": (8 * 10 ** 6, 8, 1.0), "indices": (8 * 10 ** 8, 8, 0.8), "features": (4 * 10 ** 9, 400, 0.5)}
+    plan = pkg.plan_capacities(graph, world, avail)
+    plans = [None] * world
+    dist.all_gather_object(plans, plan)
+    assert all(p == plan for p in plans)
+    assert plan["features"] == 10 ** 9 // 400 * 400 and plan["indices"] == 0 and plan["indptr"] == 0
     print("GLOO RANK %%d OK" %% rank, flush=True)
     dist.destroy_process_group()
 ''')
