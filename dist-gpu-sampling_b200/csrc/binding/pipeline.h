@@ -90,20 +90,26 @@ class BlockPipeline : public torch::CustomClassHolder {
     const auto dev = torch::Device(torch::kCUDA, static_cast<c10::DeviceIndex>(device_));
     const auto id_opt = torch::TensorOptions().dtype(indptr_->dtype()).device(dev);
     slots_.resize(depth);
-    // The sampling sequence is a chain of short, latency-bound kernels; the feature gather is one long
-    // bandwidth-bound kernel whose CTAs would otherwise queue up in front of every other batch's sampling
-    // kernels.  So each slot samples on a high-priority stream and gathers on a low-priority one: whenever an
-    // SM has room, CTAs of some batch's sampling kernels are placed first and the gather fills the rest.
+    // The sampling sequence is a chain of short kernels with thousands of CTAs each; the feature gather is one
+    // long kernel that, in its bulk-copy form, needs a single small CTA per SM for its whole duration and
+    // keeps its bytes in flight in shared memory.  Each slot therefore gathers on a stream of its own with the
+    // HIGHER priority: the gather's few CTAs are placed as soon as an SM has room and then stay out of the
+    // way, while the sampling kernels of the other batches keep filling the rest of every SM.  (With the
+    // priorities the other way round the gather waits for a gap between sampling kernels that rarely comes.)
     int prio_low = 0, prio_high = 0;
     TORCH_CHECK(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high) == cudaSuccess,
                 "BlockPipeline: cannot query stream priorities");
-    static const char* one_stream = std::getenv("DGS_PIPELINE_ONE_STREAM");  // measurement switch
+    static const char* one_stream = std::getenv("DGS_PIPELINE_ONE_STREAM");      // measurement switches
+    static const char* gather_low = std::getenv("DGS_PIPELINE_GATHER_LOW");
     const bool split = features_.defined() && !(one_stream != nullptr && one_stream[0] == '1');
+    const bool low = gather_low != nullptr && gather_low[0] == '1';
     for (Slot& s : slots_) {
-      TORCH_CHECK(cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, split ? prio_high : prio_low) == cudaSuccess,
+      TORCH_CHECK(cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, (split && low) ? prio_high : prio_low) ==
+                      cudaSuccess,
                   "BlockPipeline: cannot create a stream");
       if (split)
-        TORCH_CHECK(cudaStreamCreateWithPriority(&s.gather_stream, cudaStreamNonBlocking, prio_low) == cudaSuccess,
+        TORCH_CHECK(cudaStreamCreateWithPriority(&s.gather_stream, cudaStreamNonBlocking, low ? prio_low : prio_high) ==
+                        cudaSuccess,
                     "BlockPipeline: cannot create a stream");
       TORCH_CHECK(cudaEventCreateWithFlags(&s.ready, cudaEventDisableTiming) == cudaSuccess &&
                       cudaEventCreateWithFlags(&s.sampled, cudaEventDisableTiming) == cudaSuccess &&
@@ -265,8 +271,8 @@ class BlockPipeline : public torch::CustomClassHolder {
   static constexpr int64_t kBudgetBytes = int64_t(32) << 30;
 
   struct Slot {
-    cudaStream_t stream = nullptr;         // sampling sequence (high priority when there is a gather stream)
-    cudaStream_t gather_stream = nullptr;  // feature gather (low priority); null: everything on `stream`
+    cudaStream_t stream = nullptr;         // sampling sequence
+    cudaStream_t gather_stream = nullptr;  // feature gather (higher priority); null: everything on `stream`
     cudaEvent_t ready = nullptr, sampled = nullptr, done = nullptr;
     int64_t* sizes = nullptr;   // [2 * DGS_MAX_HOPS], pinned
     int32_t* status = nullptr;  // pinned

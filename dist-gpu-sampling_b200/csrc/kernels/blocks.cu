@@ -21,6 +21,8 @@
 // of its own.  From the second hop on the seed list is a relabel's unique list,
 // so a seed's relabelled id is its position and the sampler writes that directly;
 // only the first hop (whose seeds the caller may repeat) looks its rows up.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "launchers.h"
 
@@ -171,6 +173,14 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
   }
   DGS_CUDA_TRY(launch_chained(SITE_INIT, blocks_init_kernel, 1u, 32u, s, init));
 
+  // one-word table slots when every node id fits 32 bits (relabel_device.cuh); DGS_RELABEL_WIDE=1 keeps the
+  // two-word slots for comparison
+  static const bool force_wide = [] {
+    const char* e = std::getenv("DGS_RELABEL_WIDE");
+    return e != nullptr && e[0] == '1';
+  }();
+  const bool compact = !force_wide && (!ids64 || indptr->total - 1 < COMPACT_KEY_LIMIT);
+
   // ---- queue every hop; no size is read back in between ----
   const void* hop_seeds = seeds;
   const int64_t* n_dev = n0_dev;
@@ -184,7 +194,7 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
     const int64_t key_bound = hp.seed_bound + edge_bound;
     const Count n{hp.seed_bound, n_dev, nullptr};
     // the table is dimensioned before the neighbours are drawn: seeds * (1 + fanout) keys at most
-    const TableSize size{n, 1 + k};
+    const TableSize size{n, 1 + k, compact};
     rc = launch_sample_plan(*indptr, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h], nullptr, false,
                             make_clear_job(table[h], key_bound, size), pending, status, s);
     if (rc != DGS_OK) return rc;

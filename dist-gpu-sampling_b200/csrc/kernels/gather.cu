@@ -732,7 +732,8 @@ extern "C" int dgs_gather_rows_counted(const dgs_chunk_desc* t, const void* idx,
                                        dgs_stream_t stream) {
   using namespace dgs;
   DGS_REQUIRE(n_dev != nullptr, DGS_ERR_INVALID, "dgs_gather_rows_counted: null row count");
-  return gather_entry("dgs_gather_rows_counted", t, idx, ids64, Count{n_bound, n_dev, nullptr}, D, out, status, false, stream);
+  // queued behind a sampling sequence while other mini-batches are in flight: the form that shares the SMs
+  return gather_entry("dgs_gather_rows_counted", t, idx, ids64, Count{n_bound, n_dev, nullptr}, D, out, status, true, stream);
 }
 
 extern "C" int64_t dgs_cache_table_slots(int64_t n_keys) {

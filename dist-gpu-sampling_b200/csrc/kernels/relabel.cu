@@ -107,13 +107,38 @@ relabel_insert_kernel(const __grid_constant__ Keys keys, const TableSize size, S
   if (i >= n) return;
   const uint64_t mask = table_slots(size) - 1;
   const long long key = static_cast<long long>(keys.template load<IdT>(i));
-  if (key < 0) {
+  if (key < 0 || (size.compact && key >= COMPACT_KEY_LIMIT)) {
     raise_status(status, DGS_ERR_RANGE);
     slot_of[i] = NO_SLOT;
     return;
   }
   uint64_t h = hash_key(key) & mask;
   uint32_t found = NO_SLOT;
+  if (size.compact) {
+    unsigned long long* words = reinterpret_cast<unsigned long long*>(slots);
+    const unsigned long long mine = (static_cast<unsigned long long>(key) << 32) | static_cast<unsigned long long>(i);
+    for (uint64_t probes = 0; probes <= mask; ++probes) {
+      unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&words[h]);
+      if (cur == EMPTY_COMPACT) {
+        cur = atomicCAS(&words[h], EMPTY_COMPACT, mine);
+        if (cur == EMPTY_COMPACT) {  // claimed, and the first index is in place: nothing else to do
+          found = static_cast<uint32_t>(h);
+          break;
+        }
+      }
+      if (static_cast<long long>(cur >> 32) == key) {
+        found = static_cast<uint32_t>(h);
+        // same high half, so the minimum of the words is the minimum of the indices; a stale read can only
+        // cause a redundant atomic (indices only ever decrease)
+        if (static_cast<uint32_t>(cur) > static_cast<uint32_t>(i)) atomicMin(&words[h], mine);
+        break;
+      }
+      h = (h + 1) & mask;
+    }
+    slot_of[i] = found;
+    if (found == NO_SLOT) raise_status(status, DGS_ERR_TABLE_FULL);
+    return;
+  }
   for (uint64_t probes = 0; probes <= mask; ++probes) {
     long long cur = *reinterpret_cast<volatile long long*>(&slots[h].key);
     if (cur == EMPTY_KEY)
@@ -140,7 +165,7 @@ relabel_insert_kernel(const __grid_constant__ Keys keys, const TableSize size, S
 // the last CTA to finish turns the per-tile counts into offsets and publishes
 // the number of distinct keys
 __global__ void __launch_bounds__(RL_BLOCK)
-relabel_count_kernel(const Count nc, const Slot* __restrict__ slots,
+relabel_count_kernel(const Count nc, const Slot* __restrict__ slots, const bool compact,
                      const uint32_t* __restrict__ slot_of, int64_t* tile_sums, unsigned int* ticket,
                      int64_t* total_dev, int64_t* n_unique_out, const SizesReport report) {
   __shared__ int s_cnt;
@@ -158,7 +183,12 @@ relabel_count_kernel(const Count nc, const Slot* __restrict__ slots,
 #pragma unroll
   for (int u = 0; u < RL_ITEMS; ++u) {
     const int64_t i = base + u;
-    if (i < n && sl[u] != NO_SLOT && slots[sl[u]].val == static_cast<unsigned long long>(i)) ++c;
+    if (i < n && sl[u] != NO_SLOT) {
+      const bool first =
+          compact ? reinterpret_cast<const uint2*>(slots)[sl[u]].x == static_cast<uint32_t>(i)  // low half of the word
+                  : slots[sl[u]].val == static_cast<unsigned long long>(i);
+      if (first) ++c;
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(FULL_MASK, c, o);
@@ -175,7 +205,8 @@ relabel_count_kernel(const Count nc, const Slot* __restrict__ slots,
 // pass 3: number the first occurrences, emit them, store the label in the slot
 template <typename IdT, typename Keys>
 __global__ void __launch_bounds__(RL_BLOCK)
-relabel_number_kernel(const __grid_constant__ Keys keys, Slot* slots, const uint32_t* __restrict__ slot_of,
+relabel_number_kernel(const __grid_constant__ Keys keys, Slot* slots, const bool compact,
+                      const uint32_t* __restrict__ slot_of,
                       const int64_t* __restrict__ tile_off, IdT* __restrict__ unique_out,
                       const int64_t unique_capacity, int32_t* __restrict__ status) {
   __shared__ int smem[RL_BLOCK / 32 + 1];
@@ -195,9 +226,11 @@ relabel_number_kernel(const __grid_constant__ Keys keys, Slot* slots, const uint
     if (i >= n) slot[u] = NO_SLOT;
     if (i < n) {
       // a slot already relabelled by another CTA carries LABEL_BIT and cannot equal i
-      first[u] = slot[u] != NO_SLOT &&
-                 *reinterpret_cast<const volatile unsigned long long*>(&slots[slot[u]].val) ==
-                     static_cast<unsigned long long>(i);
+      if (slot[u] != NO_SLOT)
+        first[u] = compact ? *reinterpret_cast<const volatile uint32_t*>(reinterpret_cast<const uint2*>(slots) + slot[u]) ==
+                                 static_cast<uint32_t>(i)
+                           : *reinterpret_cast<const volatile unsigned long long*>(&slots[slot[u]].val) ==
+                                 static_cast<unsigned long long>(i);
       c += first[u] ? 1 : 0;
     }
   }
@@ -209,7 +242,8 @@ relabel_number_kernel(const __grid_constant__ Keys keys, Slot* slots, const uint
     if (first[u]) {
       if (label < unique_capacity) unique_out[label] = keys.template load<IdT>(base + u);
       else raise_status(status, DGS_ERR_RANGE);
-      slots[slot[u]].val = LABEL_BIT | static_cast<unsigned long long>(label);
+      if (compact) *reinterpret_cast<uint32_t*>(reinterpret_cast<uint2*>(slots) + slot[u]) = LABEL_BIT32 | static_cast<uint32_t>(label);
+      else slots[slot[u]].val = LABEL_BIT | static_cast<unsigned long long>(label);
       ++label;
     }
   }
@@ -219,11 +253,12 @@ relabel_number_kernel(const __grid_constant__ Keys keys, Slot* slots, const uint
 template <typename IdT>
 __global__ void __launch_bounds__(RL_BLOCK)
 relabel_lookup_kernel(const __grid_constant__ dgs_segments in, const int64_t n,
-                      const Slot* __restrict__ slots, const uint64_t mask, IdT* __restrict__ out) {
+                      const Slot* __restrict__ slots, const uint64_t mask, const bool compact,
+                      IdT* __restrict__ out) {
   pdl_enter();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * RL_BLOCK + threadIdx.x;
   if (i >= n) return;
-  out[i] = static_cast<IdT>(probe_label(slots, mask, static_cast<long long>(seg_load<IdT>(in, i))));
+  out[i] = static_cast<IdT>(probe_label(slots, mask, static_cast<long long>(seg_load<IdT>(in, i)), compact));
 }
 
 // lookup of the sequence with device-side counts, when it does not ride on another launch
@@ -259,9 +294,10 @@ int run_unique(const Keys& keys, Count n_keys, const TableSize& size, const Tabl
   DGS_CUDA_TRY(launch_chained(SITE_INSERT, relabel_insert_kernel<IdT, Keys>, per_key_grid, RL_BLOCK, s, keys, size, t.slots,
                               t.slot_of, status));
   DGS_CUDA_TRY(launch_chained(SITE_COUNT, relabel_count_kernel, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, n_keys, t.slots,
-                              t.slot_of, t.tile_off, t.ticket, t.total, n_unique, report));
+                              size.compact, t.slot_of, t.tile_off, t.ticket, t.total, n_unique, report));
   DGS_CUDA_TRY(launch_chained(SITE_NUMBER, relabel_number_kernel<IdT, Keys>, static_cast<unsigned>(t.ntiles), RL_BLOCK, s, keys,
-                              t.slots, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out), unique_capacity, status));
+                              t.slots, size.compact, t.slot_of, t.tile_off, static_cast<IdT*>(unique_out), unique_capacity,
+                              status));
   return DGS_OK;
 }
 
@@ -347,7 +383,8 @@ extern "C" int dgs_unique_first_occurrence(const dgs_segments* keys, int32_t ids
   DGS_CUDA_TRY(cudaMemsetAsync(t.slots, 0xFF, t.cap * sizeof(Slot), s));
   DGS_CUDA_TRY(cudaMemsetAsync(t.ticket, 0, sizeof(unsigned int), s));
   const SegKeys sk{*keys, n};
-  const TableSize size{exact_count(n), 1};
+  // 32-bit ids always fit the one-word slots; for 64-bit ids this entry point knows nothing about the id space
+  const TableSize size{exact_count(n), 1, ids64 == 0};
   return ids64 ? run_unique<int64_t, SegKeys>(sk, exact_count(n), size, t, unique_out, n, n_unique, SizesReport{},
                                               status, s)
                : run_unique<int32_t, SegKeys>(sk, exact_count(n), size, t, unique_out, n, n_unique, SizesReport{},
@@ -371,9 +408,9 @@ extern "C" int dgs_relabel_lookup(const void* table, size_t table_bytes, int64_t
   const unsigned grid = static_cast<unsigned>((n + RL_BLOCK - 1) / RL_BLOCK);
   if (ids64)
     DGS_CUDA_TRY(launch_chained(SITE_LOOKUP, relabel_lookup_kernel<int64_t>, grid, RL_BLOCK, s, *in, n, t.slots, t.cap - 1,
-                                static_cast<int64_t*>(out)));
-  else
+                                false, static_cast<int64_t*>(out)));
+  else  // the table of dgs_unique_first_occurrence for 32-bit ids has one-word slots
     DGS_CUDA_TRY(launch_chained(SITE_LOOKUP, relabel_lookup_kernel<int32_t>, grid, RL_BLOCK, s, *in, n, t.slots, t.cap - 1,
-                                static_cast<int32_t*>(out)));
+                                true, static_cast<int32_t*>(out)));
   return DGS_OK;
 }

@@ -18,6 +18,17 @@ struct __align__(16) Slot {
   unsigned long long val;
 };
 
+// Compact tables: when every key is below 2^32 - 1 (32-bit ids, or 64-bit ids of a graph with fewer nodes
+// than that) a slot is ONE 64-bit word, key in the high half and the minimum input index (later the label)
+// in the low half.  Claiming a slot and setting its first index is then a single compare-and-swap, a
+// repeated key costs one load and at most one atomicMin, and every later pass reads 8 bytes per key instead
+// of 16; the table (and the clearing of it) is half the size.  Input indices and labels stay below 2^30
+// (the key count is limited to that), so bit 31 of the low half marks a label.  The same memory holds
+// either form: a table laid out for `cap` 16-byte slots uses its first half as `cap` compact slots.
+constexpr unsigned long long EMPTY_COMPACT = ~0ull;
+constexpr uint32_t LABEL_BIT32 = 0x80000000u;
+constexpr long long COMPACT_KEY_LIMIT = 0xFFFFFFFFll;  // keys must be below this
+
 // slots in use for a table built for n keys: the power of two >= max(2n, 64)
 __host__ __device__ __forceinline__ uint64_t slots_for(int64_t n) {
   uint64_t want = 2 * static_cast<uint64_t>(n);
@@ -37,6 +48,7 @@ __host__ __device__ __forceinline__ uint64_t slots_for(int64_t n) {
 struct TableSize {
   Count n;
   int64_t mult;
+  bool compact;  // one-word slots (see above)
 };
 
 // Sizes that only the host needs (how much of each output is valid): device words copied to a
@@ -59,9 +71,21 @@ __device__ __forceinline__ uint64_t hash_key(long long key) {
   return z ^ (z >> 33);
 }
 
-__device__ __forceinline__ long long probe_label(const Slot* __restrict__ slots, uint64_t mask, long long key) {
+__device__ __forceinline__ long long probe_label(const Slot* __restrict__ slots, uint64_t mask, long long key,
+                                                 bool compact) {
   if (key < 0) return -1;
   uint64_t h = hash_key(key) & mask;
+  if (compact) {
+    if (key >= COMPACT_KEY_LIMIT) return -1;
+    const unsigned long long* __restrict__ words = reinterpret_cast<const unsigned long long*>(slots);
+    for (uint64_t probes = 0; probes <= mask; ++probes) {
+      const unsigned long long w = words[h];  // one 8-byte load
+      if (static_cast<long long>(w >> 32) == key) return static_cast<long long>(static_cast<uint32_t>(w) & ~LABEL_BIT32);
+      if (w == EMPTY_COMPACT) break;
+      h = (h + 1) & mask;
+    }
+    return -1;
+  }
   for (uint64_t probes = 0; probes <= mask; ++probes) {
     const Slot s = slots[h];  // one 16-byte load
     if (s.key == key) return static_cast<long long>(s.val & ~LABEL_BIT);
@@ -79,7 +103,8 @@ struct ClearJob {
   unsigned ctas;  // CLEAR_SLOTS_PER_CTA slots each; 0: no job
 };
 __device__ __forceinline__ void run_clear_cta(const ClearJob& j, unsigned cta) {
-  const uint64_t cap = table_slots(j.size);
+  // in 16-byte units: compact slots are half as wide
+  const uint64_t cap = j.size.compact ? table_slots(j.size) / 2 : table_slots(j.size);
   const uint64_t i = static_cast<uint64_t>(cta) * CLEAR_SLOTS_PER_CTA + threadIdx.x;
   const ulonglong2 empty = make_ulonglong2(~0ull, ~0ull);
 #pragma unroll
@@ -110,8 +135,8 @@ __device__ __forceinline__ void run_lookup_cta(const LookupJob& j, unsigned cta)
   const long long kb = in_bound ? static_cast<long long>(static_cast<const IdT*>(j.b)[i]) : -1;
   if (i >= count_of(j.n)) return;
   const uint64_t mask = table_slots(j.size) - 1;
-  if (j.a != nullptr) static_cast<IdT*>(j.out_a)[i] = static_cast<IdT>(probe_label(j.slots, mask, ka));
-  static_cast<IdT*>(j.out_b)[i] = static_cast<IdT>(probe_label(j.slots, mask, kb));
+  if (j.a != nullptr) static_cast<IdT*>(j.out_a)[i] = static_cast<IdT>(probe_label(j.slots, mask, ka, j.size.compact));
+  static_cast<IdT*>(j.out_b)[i] = static_cast<IdT>(probe_label(j.slots, mask, kb, j.size.compact));
 }
 
 #endif  // __CUDACC__
