@@ -115,7 +115,7 @@ def parse_args():
     ap.add_argument("--api", default="pipeline", choices=["pipeline", "blocks", "per-hop"],
                     help="which of the three ways through the library is the headline `value`; the other two are "
                          "timed too and reported under other_api")
-    ap.add_argument("--depth", type=int, default=3, help="batches in flight in the pipeline")
+    ap.add_argument("--depth", type=int, default=6, help="batches in flight in the pipeline")
     ap.add_argument("--no-extra-configs", action="store_true",
                     help="skip the short Papers100M-shaped measurement at the end of a default run")
     ap.add_argument("--extra-steps", type=int, default=200, help="timed steps of that extra measurement")
@@ -177,10 +177,14 @@ class ClockSampler:
 
 
 def build_graph(w, device):
-    """Same seeded graph on every rank (generated on `device`)."""
+    """Same seeded graph on every rank (generated on `device`).  Workloads that keep part of their tensors in the
+    host tail get their node ids ranked by in-degree with the library's own renumbering step (hot rows first, so
+    that they land in the GPU chunks) -- what a user with a real graph would call before creating ChunkTensors."""
+    pkg = importlib.import_module("dist-gpu-sampling_b200")
     synth = importlib.import_module("dist-gpu-sampling_b200.synth")
-    indptr, indices = synth.chung_lu_csc(w["nodes"], w["mean_deg"], w["gamma"], seed=11, device=device,
-                                         degree_sorted=w["degree_sorted"])
+    indptr, indices = synth.chung_lu_csc(w["nodes"], w["mean_deg"], w["gamma"], seed=11, device=device)
+    if w["degree_sorted"]:
+        indptr, indices, _, _ = pkg.renumber_by_degree(indptr, indices, by="in", with_edge_source=False)
     return indptr, indices
 
 
@@ -770,7 +774,11 @@ def roofline_dict(res, w, peaks, hbm_peak, hbm_kind):
                 "local": {"rows": n_loc, "bytes": n_loc * (8 + 2 * row_bytes), "bytes_per_row": 8 + 2 * row_bytes,
                           "peak_gbs": hbm_peak, "t_ms": t["hbm"] * 1e3},
                 "peer": {"rows": n_peer, "bytes": b_nvl, "bytes_per_row": row_bytes, "peak_gbs": nvl_peak,
-                         "t_ms": t["nvlink"] * 1e3, "achieved_gbs_if_alone": b_nvl / (ms * 1e-3) / 1e9},
+                         "t_ms": t["nvlink"] * 1e3, "achieved_gbs_if_alone": b_nvl / (ms * 1e-3) / 1e9,
+                         # a row that starts on a 16-byte boundary covers this many 128-byte lines, each one
+                         # read request on the link; the link moves requests, not bytes, at a fixed rate
+                         "line_requests_per_row": -(-(row_bytes + 112) // 128),
+                         "line_requests_per_s": n_peer * (-(-(row_bytes + 112) // 128)) / (ms * 1e-3)},
                 "host": {"rows": n_host, "bytes": b_host, "bytes_per_row": row_bytes, "peak_gbs": host_peak,
                          "t_ms": t["host"] * 1e3}},
             "traffic": per_row * rows if (per_row and bound == "hbm") else None}

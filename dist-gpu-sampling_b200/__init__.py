@@ -255,7 +255,7 @@ class PipelinedSampler:
     """Mini-batches in flight: the role DGL's DataLoader plays around ChunkTensorSampler in the reference
     (oppo_bench/single_node/chunktensor.py:120-172), on torch.classes.dgs_classes.BlockPipeline.
 
-        sampler = PipelinedSampler(indptr_ct, indices_ct, [15, 10, 5], features=feat_ct, max_seeds=1024, depth=3)
+        sampler = PipelinedSampler(indptr_ct, indices_ct, [15, 10, 5], features=feat_ct, max_seeds=1024, depth=6)
         for input_nodes, blocks, n_edges, x in sampler(seed_batches):
             ...   # blocks = [(coo_row, coo_col, n_src, n_dst)] in layer order, x = features[input_nodes]
 
@@ -269,7 +269,7 @@ class PipelinedSampler:
     Delete the sampler before the ChunkTensors it reads (their destructor is collective).
     """
 
-    def __init__(self, indptr, indices, fanouts, features=None, probs=None, replace=False, max_seeds=1024, depth=3):
+    def __init__(self, indptr, indices, fanouts, features=None, probs=None, replace=False, max_seeds=1024, depth=6):
         import torch
         load_ops()
         self.depth = int(depth)

@@ -531,6 +531,11 @@ int launch_gather_bulk(const Src& rows, Count nc, int64_t D, int sh, void* out, 
   const int64_t groups = (nc.bound + group - 1) / group;
   int64_t grid = (groups + BULK_WARPS - 1) / BULK_WARPS;
   if (grid > static_cast<int64_t>(sms) * per_sm) grid = static_cast<int64_t>(sms) * per_sm;
+  static const int grid_cap = [] {  // measurement switch: fewer CTAs = fewer copies in flight
+    const char* e = std::getenv("DGS_GATHER_BULK_GRID");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  if (grid_cap > 0 && grid > grid_cap) grid = grid_cap;
   auto kernel = gather_rows_bulk_kernel<Src>;
   static bool smem_opted_in = false;  // per instantiation; the buffers never exceed 12 x 8 KB + the barriers
   if (!smem_opted_in) {

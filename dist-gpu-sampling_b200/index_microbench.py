@@ -14,8 +14,8 @@ with a bandwidth measured on the machine it runs on.
       dist-gpu-sampling_b200/index_microbench.py --rows 8000000 --host-frac 0.2 \
       --ids 1000,16000,256000,1000000,4000000 --dist zipf
 
---ids takes a list (one query size after the other on the same table), --dist uniform|zipf picks the id
-distribution (Zipf(1.1) ranks mapped to rows by a fixed permutation), --misalign B adds B bytes to the
+--ids takes a list (one query size after the other on the same table), --dist uniform|zipf|uniform,zipf picks
+the id distribution (Zipf(1.1) ranks mapped to rows by a fixed permutation), --misalign B adds B bytes to the
 capacity so that chunk boundaries fall inside rows (the straddle and off-grid paths of the gather).
 
 The table is filled in place, chunk by chunk, with a hash of the flat element
@@ -39,7 +39,8 @@ def main():
     ap.add_argument("--ids", type=str, default="1000000",
                     help="row ids per query; a comma-separated list runs one query size after the other")
     ap.add_argument("--host-frac", type=float, default=0.0, help="fraction of rows kept in the host tail")
-    ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"])
+    ap.add_argument("--dist", default="uniform",
+                    help="uniform | zipf | uniform,zipf (both, one after the other on the same table)")
     ap.add_argument("--id-window", type=int, default=0,
                     help="draw the ids from a window of this many rows at the start of the next rank's chunk "
                          "(all remote, one peer, limited address range); 0 = whole table")
@@ -47,6 +48,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--hbm-peak", type=float, default=0.0, help="GB/s; 0 = measure a device copy here")
+    ap.add_argument("--nvlink-peak", type=float, default=770.0,
+                    help="GB/s per direction the peer class is compared with (default: a measured peer copy on B200)")
     args = ap.parse_args()
 
     import torch
@@ -86,9 +89,15 @@ def main():
         dist.barrier()
 
     id_counts = [int(x) for x in str(args.ids).split(",")]
+    dists = [d for d in str(args.dist).split(",") if d]
+    for d in dists:
+        if d not in ("uniform", "zipf"):
+            raise SystemExit("--dist: uniform, zipf or uniform,zipf")
     hbm_cached = [args.hbm_peak]
-    for n_ids in id_counts:
-        run_query(args, n_ids, table, sub, host, each, world, rank, dev, synth, torch, hbm_cached)
+    for d in dists:
+        args.dist = d
+        for n_ids in id_counts:
+            run_query(args, n_ids, table, sub, host, each, world, rank, dev, synth, torch, hbm_cached)
     del table, sub, host
     if world > 1:
         dist.barrier()
@@ -156,7 +165,7 @@ def run_query(args, n_ids, table, sub, host, each, world, rank, dev, synth, torc
 
     cases = [("index (mixed)", table._CAPI_index, ids, None),
              ("local_index", table._CAPI_local_index, lo_ids, hbm),
-             ("remote_index", table._CAPI_remote_index, re_ids, 770.0),
+             ("remote_index", table._CAPI_remote_index, re_ids, args.nvlink_peak),
              ("host_index", table._CAPI_host_index, ho_ids, host_link)]
     solo = os.environ.get("DGS_MB_SOLO_RANK")       # only this rank issues requests, the others just serve
     for name, fn, idx, peak in cases:

@@ -67,7 +67,7 @@ def plan_capacities(tensors, num_gpus, available_mem, priority=CACHE_PRIORITY, w
     return plan
 
 
-def renumber_by_degree(indptr, indices, by="in", edge_chunk=1 << 27):
+def renumber_by_degree(indptr, indices, by="in", edge_chunk=1 << 27, with_edge_source=True):
     """Renumber the nodes of a CSC graph by descending degree, so that the hottest rows get the smallest ids and
     land in the GPU chunks of a ChunkTensor that caches only part of a tensor.
 
@@ -79,8 +79,8 @@ def renumber_by_degree(indptr, indices, by="in", edge_chunk=1 << 27):
     Returns (new_indptr, new_indices, old_of_new, edge_source):
       old_of_new[i] = old id of new node i   (node tensors: features_new = features[old_of_new])
       edge_source[p] = old position of new edge p   (edge tensors: probs_new = probs[edge_source]);
-                       None when the graph has more than `edge_chunk` * 8 edges (call permute_edge_tensor
-                       with the returned node order instead).
+                       None when with_edge_source is False or the graph has more than `edge_chunk` * 8
+                       edges (call permute_edge_tensor with the returned node order instead).
     Row i of the new graph holds the neighbours of old node old_of_new[i], in the old order, renamed.
     """
     import torch
@@ -103,7 +103,7 @@ def renumber_by_degree(indptr, indices, by="in", edge_chunk=1 << 27):
     torch.cumsum(new_deg, 0, out=new_indptr[1:])
     e_total = int(new_indptr[-1])
     new_indices = torch.empty(e_total, dtype=indices.dtype, device=dev)
-    keep_source = e_total <= 8 * edge_chunk
+    keep_source = with_edge_source and e_total <= 8 * edge_chunk
     edge_source = torch.empty(e_total, dtype=torch.int64, device=dev) if keep_source else None
     old_begin = indptr[:-1][old_of_new]
     row = 0

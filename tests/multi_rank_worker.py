@@ -144,6 +144,7 @@ def main():
     assert torch.ops.dgs_ops._CAPI_get_current_allocated() > 0
     torch.cuda.synchronize()
     dist.barrier()
+    del pr                                 # (a second name for one of the ChunkTensors)
     del c_ip2, c_ix2, c_pr2, c_ft2
     del ct, c_ip, c_ix, c_pr, sub          # collective teardown, same order everywhere
     assert torch.ops.dgs_ops._CAPI_get_current_allocated() == 0
