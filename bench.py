@@ -223,7 +223,8 @@ def config_dict(args, w, n_edges_graph, world):
             "train_set": w["train"], "replace": False, "weighted": bool(args.weighted),
             "step": "sample_blocks over %d hops = %d x (%s + tensor_relabel), then features._CAPI_index(input_nodes)"
                     % (len(w["fanouts"]), len(w["fanouts"]), op),
-            "storage": "indptr/indices/features in ChunkTensors split evenly over %d GPU(s), %s" % (world, tail),
+            "storage": "indptr/indices/features in ChunkTensors split evenly over %d GPU(s) in whole rows "
+                       "(the up to N-1 rows that do not divide evenly sit in the host tail), %s" % (world, tail),
             "l2": "inputs larger than L2 (indices %.2f GB, features %.2f GB); a new seed batch every step"
                   % (n_edges_graph * 8 / 1e9, nodes * dim * 4 / 1e9)}
 
@@ -419,6 +420,7 @@ def setup_workload(env, args, w, want_host_graph):
     """ChunkTensors of one workload, filled in place; returns an object with everything a measurement needs."""
     import torch
     import torch.distributed as dist
+    pkg = importlib.import_module("dist-gpu-sampling_b200")
     synth = importlib.import_module("dist-gpu-sampling_b200.synth")
     dev, world, rank = env.dev, env.world, env.rank
     nodes, dim = w["nodes"], w["dim"]
@@ -426,9 +428,14 @@ def setup_workload(env, args, w, want_host_graph):
     n_edges_graph = int(indices.numel())
     fill = 1 << 26
 
-    def chunk_capacity(nbytes, frac=1.0):
-        cap = -(-int(nbytes * frac) // world)
-        return -(-cap // 16) * 16
+    def chunk_capacity(nbytes, row_bytes, frac=1.0):
+        """An equal share per GPU, cut to whole rows (the package's create_chunktensor rule): with a capacity
+        that is not a whole number of rows the reference's placement arithmetic (src/chunk_tensor.cc:57-68) puts
+        the rows of every later chunk off the 16-byte grid and the gather has to fall back to narrow loads.  The
+        rows that do not divide evenly (at most world - 1 of them) end up in the host tail."""
+        if world == 1 and frac >= 1.0:
+            return nbytes
+        return pkg.cached_size_per_gpu(nbytes, world, 1 << 62, frac, row_bytes)
 
     def fill_chunk(ct, total, values):
         """values(start, count) -> device tensor of the flat elements [start, start+count)."""
@@ -447,8 +454,9 @@ def setup_workload(env, args, w, want_host_graph):
 
     def to_chunk(t, frac=1.0):
         flat = t.reshape(-1)
+        row_bytes = t.element_size() * (t.shape[1] if t.dim() == 2 else 1)
         ct = torch.classes.dgs_classes.ChunkTensor(list(t.shape), t.dtype,
-                                                   chunk_capacity(flat.numel() * t.element_size(), frac))
+                                                   chunk_capacity(flat.numel() * t.element_size(), row_bytes, frac))
         return fill_chunk(ct, flat.numel(), lambda start, count: flat[start:start + count])
 
     wl = Env()
@@ -457,11 +465,12 @@ def setup_workload(env, args, w, want_host_graph):
     wl.c_indices = to_chunk(indices, w["gpu_frac"])
     wl.c_probs = None
     if args.weighted:
-        wl.c_probs = torch.classes.dgs_classes.ChunkTensor([n_edges_graph], torch.float32, chunk_capacity(n_edges_graph * 4))
+        wl.c_probs = torch.classes.dgs_classes.ChunkTensor([n_edges_graph], torch.float32,
+                                                           chunk_capacity(n_edges_graph * 4, 4))
         fill_chunk(wl.c_probs, n_edges_graph, lambda start, count: edge_weights(start, count, dev))
     # features: every rank fills its own chunk in place
     wl.c_feats = torch.classes.dgs_classes.ChunkTensor([nodes, dim], torch.float32,
-                                                       chunk_capacity(nodes * dim * 4, w["gpu_frac"]))
+                                                       chunk_capacity(nodes * dim * 4, dim * 4, w["gpu_frac"]))
     fill_chunk(wl.c_feats, nodes * dim, lambda start, count: feature_values(start, count, dev))
     wl.host_graph = None
     if want_host_graph:
@@ -638,8 +647,14 @@ def measure_workload(env, args, pkg, wl, steps, warmup, full):
     res["blocks"], res["per-hop"] = blocks_t, perhop_t
 
     # ---- end to end: seeds from pinned host memory, the step's result read back ----
+    chk_host = torch.zeros((64, 2), dtype=torch.float32).pin_memory()
+    chk_state = {"i": 0}
+
     def checksum(fr, blocks, x):
-        torch.stack([x.sum(), fr.sum().to(torch.float32)]).cpu()      # 8 bytes leave the device every step
+        # 8 bytes leave the device every step, into a ring of pinned words; the copies are asynchronous, the
+        # barrier that closes the timed region waits for all of them
+        chk_host[chk_state["i"] % 64].copy_(torch.stack([x.sum(), fr.sum().to(torch.float32)]), non_blocking=True)
+        chk_state["i"] += 1
     timed_pipeline(host_batches, batch_ids(0, min(n_warm, 5)), checksum)
     e2e_ms, e2e_edges, _ = timed_pipeline(host_batches, ids, checksum)
     res["e2e"] = {"ms": e2e_ms, "edges": e2e_edges, "d2h_bytes_per_step": 8 + 8 * 2 * H}

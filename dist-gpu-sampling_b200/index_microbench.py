@@ -69,7 +69,10 @@ def main():
 
     D, rows = args.dim, args.rows
     gpu_rows = int(rows * (1.0 - args.host_frac))
-    cap = -(-gpu_rows // world) * D * 4 + args.misalign
+    # whole rows per GPU, rounded DOWN: a capacity that covers the whole table makes the placement rule
+    # (src/chunk_tensor.cc:57-68) recompute the chunk as ceil(elements / world), which cuts a row in two
+    # whenever the row count does not divide evenly, and every later chunk then starts off the 16-byte grid
+    cap = (gpu_rows // world) * D * 4 + args.misalign
     table = torch.classes.dgs_classes.ChunkTensor([rows, D], torch.float32, cap)
     sub = table._CAPI_get_sub_device_tensor()
     each = sub.numel()
