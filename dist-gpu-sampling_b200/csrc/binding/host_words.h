@@ -9,7 +9,7 @@
 // its own words, so calls from several host threads, or on several streams, do
 // not see each other's sizes or errors.
 //
-// Status semantics (also stated in INTEGRATION.md):
+// Status semantics:
 //   * an error raised by a kernel that has finished by the time the operator
 //     learns its sizes is thrown by that operator call;
 //   * an error raised later (kernels still running when the operator returns, or

@@ -92,9 +92,14 @@ struct ChunkRows {
   int64_t n_rows_total;  // rows lying fully inside the tensor
   int sh;
 
+  // the requested row id at position i, and where that row lives
+  __device__ __forceinline__ int64_t row_id(int64_t i) const { return static_cast<int64_t>(idx[i]); }
   template <int VEC, bool REALIGN>
   __device__ __forceinline__ const char* locate(int64_t i, int32_t* status) const {
-    const int64_t row = static_cast<int64_t>(idx[i]);
+    return locate_row<VEC, REALIGN>(row_id(i), status);
+  }
+  template <int VEC, bool REALIGN>
+  __device__ __forceinline__ const char* locate_row(int64_t row, int32_t* status) const {
     if (row < 0 || row >= n_rows_total) {
       raise_status(status, DGS_ERR_RANGE);
       return DGS_ROW_ZERO;
@@ -418,11 +423,17 @@ gather_rows_bulk_kernel(const __grid_constant__ Src rows, const int64_t n_bound,
   const int64_t stride = static_cast<int64_t>(gridDim.x) * BULK_WARPS;
   const int64_t first = static_cast<int64_t>(blockIdx.x) * BULK_WARPS + warp;
 
-  // loads of group g into stage st
-  auto issue = [&](int64_t g, int st) {
+  // the row id lane `lane` will need for group g (read one iteration before the group is issued, so that
+  // the warp never waits for it)
+  auto fetch_id = [&](int64_t g) -> int64_t {
+    const int64_t i = g * group + lane;
+    return (g < n_groups && lane < static_cast<int>(group) && i < n) ? rows.row_id(i) : 0;
+  };
+  // loads of group g into stage st; row = what fetch_id(g) returned
+  auto issue = [&](int64_t g, int st, int64_t row) {
     const int64_t i = g * group + lane;
     const bool valid = lane < static_cast<int>(group) && i < n;
-    const char* src = valid ? rows.template locate<16, false>(i, status) : nullptr;
+    const char* src = valid ? rows.template locate_row<16, false>(row, status) : nullptr;
     const bool whole = valid && reinterpret_cast<uintptr_t>(src) > 1;
     const uint32_t bar = smem_addr(bars + st);
     unsigned char* slot = my_stages + static_cast<size_t>(st) * stage_bytes + static_cast<size_t>(lane) * row_bytes;
@@ -456,9 +467,10 @@ gather_rows_bulk_kernel(const __grid_constant__ Src rows, const int64_t n_bound,
   int64_t g_issue = first;
 #pragma unroll
   for (int s = 0; s < BULK_STAGES - 1; ++s) {
-    if (g_issue < n_groups) issue(g_issue, s);
+    if (g_issue < n_groups) issue(g_issue, s, fetch_id(g_issue));
     g_issue += stride;
   }
+  int64_t next_row = fetch_id(g_issue);  // for the group the first iteration will issue
   uint32_t phase_bits = 0;  // parity of each stage's barrier
   int st = 0, st_issue = BULK_STAGES - 1;
   bool alive = true;
@@ -481,7 +493,9 @@ gather_rows_bulk_kernel(const __grid_constant__ Src rows, const int64_t n_bound,
       bulk_wait_read<1>();
     }
     __syncwarp();
-    if (g_issue < n_groups) issue(g_issue, st_issue);
+    const int64_t row_now = next_row;
+    next_row = fetch_id(g_issue + stride);  // in flight while this iteration's copies are issued and awaited
+    if (g_issue < n_groups) issue(g_issue, st_issue, row_now);
     g_issue += stride;
     st = st + 1 == BULK_STAGES ? 0 : st + 1;
     st_issue = st_issue + 1 == BULK_STAGES ? 0 : st_issue + 1;
