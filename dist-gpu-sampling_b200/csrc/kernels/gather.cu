@@ -377,15 +377,36 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
-// global -> shared, `bytes` a multiple of 16, both addresses 16-byte aligned; no multicast
-__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
+// L2 policy "evict first" for data that streams through once: gathered rows and the output they are written
+// to should not push the relabel tables and plan arrays of the sampling kernels (which run at the same time,
+// for other mini-batches) out of the L2
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
 }
-__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
-               : "memory");
+// global -> shared, `bytes` a multiple of 16, both addresses 16-byte aligned; no multicast
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar,
+                                          uint64_t policy, bool hinted) {
+  if (hinted)
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            dst_smem),
+        "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+  else
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes, uint64_t policy, bool hinted) {
+  if (hinted)
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::"l"(dst), "r"(src_smem),
+                 "r"(bytes), "l"(policy)
+                 : "memory");
+  else
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+                 : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 template <int N>
@@ -399,8 +420,10 @@ template <typename Src>
 __global__ void __launch_bounds__(BULK_WARPS * 32)
 gather_rows_bulk_kernel(const __grid_constant__ Src rows, const int64_t n_bound, const int64_t* __restrict__ n_dev,
                         const int64_t D, const int sh, const uint32_t row_bytes, const uint32_t group,
-                        const uint32_t stage_bytes, char* __restrict__ out, int32_t* __restrict__ status) {
+                        const uint32_t stage_bytes, const bool l2_hint, char* __restrict__ out,
+                        int32_t* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char bulk_smem[];
+  const uint64_t policy = l2_evict_first_policy();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   unsigned char* my_stages = bulk_smem + static_cast<size_t>(warp) * BULK_STAGES * stage_bytes;
@@ -441,7 +464,7 @@ gather_rows_bulk_kernel(const __grid_constant__ Src rows, const int64_t n_bound,
     if (lane == 0) mbar_expect_tx(bar, expect);  // also the one arrival the barrier waits for
     __syncwarp();
     if (whole) {
-      bulk_load(smem_addr(slot), src, row_bytes, bar);
+      bulk_load(smem_addr(slot), src, row_bytes, bar, policy, l2_hint);
     } else if (valid) {
       // rare: zero row (bad id) or a row that straddles two storage regions, element by element
       const int esz = 1 << sh;
@@ -488,7 +511,7 @@ gather_rows_bulk_kernel(const __grid_constant__ Src rows, const int64_t n_bound,
       const int64_t row0 = g * group;
       const int64_t rows_here = n - row0 < static_cast<int64_t>(group) ? n - row0 : static_cast<int64_t>(group);
       bulk_store(out + row0 * row_bytes, smem_addr(my_stages + static_cast<size_t>(st) * stage_bytes),
-                 static_cast<uint32_t>(rows_here) * row_bytes);
+                 static_cast<uint32_t>(rows_here) * row_bytes, policy, l2_hint);
       // the buffer that is loaded next was stored from one iteration ago: that store must have read it
       bulk_wait_read<1>();
     }
@@ -566,8 +589,12 @@ int launch_gather_bulk(const Src& rows, Count nc, int64_t D, int sh, void* out, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = chained_launches_enabled(SITE_GATHER) ? 1 : 0;
+  static const bool l2_hint = [] {  // DGS_GATHER_L2_HINT=0: default L2 policy, for comparison
+    const char* e = std::getenv("DGS_GATHER_L2_HINT");
+    return !(e != nullptr && e[0] == '0');
+  }();
   DGS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, rows, nc.bound, nc.dev, D, sh, static_cast<uint32_t>(row_bytes), group,
-                                  stage_bytes, static_cast<char*>(out), status));
+                                  stage_bytes, l2_hint, static_cast<char*>(out), status));
   return DGS_OK;
 }
 
