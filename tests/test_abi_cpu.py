@@ -223,3 +223,38 @@ def test_sample_blocks_rejects_bad_arguments_before_any_launch(abi, pkg):
     big[0].coo_row = big[0].coo_col = big[0].frontier = 0x2000
     assert call(probs=ctypes.byref(pr), hops=big, n_hops=1,
                 ws_bytes=abi.dgs_sample_blocks_workspace_bytes(big, 1)) == UNSUPPORTED      # weighted fan-out > 32
+
+
+def test_counted_gather_and_frontier_count_reject_bad_arguments_before_any_launch(abi, pkg):
+    """dgs_gather_rows_counted / dgs_sample_blocks_frontier_count: argument errors are codes (or NULL) with a
+    message, and the frontier-count word lies inside the workspace the caller passes; nothing reaches CUDA."""
+    d = pkg.ChunkDesc()
+    d.total = d.threshold = d.each = 4000
+    d.num_parts, d.esz = 1, 4
+    d.dev[0] = 0x1000                        # never dereferenced on the host
+    INVALID = 1
+    word = ctypes.c_void_p(0x5000)
+    assert abi.dgs_gather_rows_counted(ctypes.byref(d), 0x2000, 1, 10, None, 100, 0x3000, None, None) == INVALID
+    assert b"row count" in abi.dgs_last_error()
+    assert abi.dgs_gather_rows_counted(None, 0x2000, 1, 10, word, 100, 0x3000, None, None) == INVALID
+    assert abi.dgs_gather_rows_counted(ctypes.byref(d), 0x2000, 1, -1, word, 100, 0x3000, None, None) == INVALID
+    assert abi.dgs_gather_rows_counted(ctypes.byref(d), 0x2000, 1, 10, word, 0, 0x3000, None, None) == INVALID
+    assert abi.dgs_gather_rows_counted(ctypes.byref(d), None, 1, 10, word, 100, 0x3000, None, None) == INVALID
+    assert abi.dgs_gather_rows_counted(ctypes.byref(d), 0x2000, 1, 0, word, 100, None, None, None) == 0   # nothing to do
+
+    hops = (pkg.Hop * 3)()
+    assert abi.dgs_sample_blocks_bounds(1024, (ctypes.c_int64 * 3)(5, 10, 15), 3, 2_449_029, hops) == 0
+    ws_bytes = abi.dgs_sample_blocks_workspace_bytes(hops, 3)
+    base = 0x10000000
+    at = abi.dgs_sample_blocks_frontier_count(hops, 3, base)
+    assert at is not None and base < at < base + ws_bytes and at % 8 == 0
+    # it sits in the last hop's table: behind the two earlier hops' plans and tables and the last hop's plan
+    skipped = 256
+    for h in hops[:2]:
+        skipped += -(-abi.dgs_sample_plan_bytes(h.seed_bound) // 256) * 256
+        skipped += -(-abi.dgs_relabel_table_bytes(h.seed_bound * (1 + h.fanout)) // 256) * 256
+    skipped += -(-abi.dgs_sample_plan_bytes(hops[2].seed_bound) // 256) * 256
+    assert at - base > skipped
+    assert abi.dgs_sample_blocks_frontier_count(None, 3, base) is None
+    assert abi.dgs_sample_blocks_frontier_count(hops, 0, base) is None
+    assert abi.dgs_sample_blocks_frontier_count(hops, 3, None) is None
