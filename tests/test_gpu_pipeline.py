@@ -83,16 +83,18 @@ def test_pipeline_stochastic_batches_are_valid_and_results_outlive_later_submits
     del sampler
 
 
-def test_pipeline_weighted_and_without_features(ops, oracle, pkg):
+@pytest.mark.parametrize("weighted,replace", [(True, False), (True, True), (False, True)])
+def test_pipeline_weighted_replace_and_without_features(ops, oracle, pkg, weighted, replace):
     rng = np.random.default_rng(23)
     indptr, indices = graph(rng, 8000, 60, hubs=(5000,))
     probs = (rng.random(indices.size) + 0.05).astype(np.float32)
     c_ip, c_ix, c_pr = chunked(indptr), chunked(indices, 0.7), chunked(probs, 0.7)
     batches = [rng.permutation(8000)[:256] for _ in range(4)]
-    sampler = pkg.PipelinedSampler(c_ip, c_ix, [10, 10], probs=c_pr, max_seeds=256, depth=2)
+    sampler = pkg.PipelinedSampler(c_ip, c_ix, [10, 10], probs=c_pr if weighted else None, replace=replace,
+                                   max_seeds=256, depth=2)
     for (f, blocks, ne, x), seeds in zip(sampler(to_dev(b) for b in batches), batches):
         assert x.numel() == 0
-        assert ne == check_hops(oracle, indptr, indices, seeds, [10, 10], False, f, blocks)
+        assert ne == check_hops(oracle, indptr, indices, seeds, [10, 10], replace, f, blocks)
     del sampler
 
 
