@@ -111,18 +111,34 @@ sample_plan_kernel(const __grid_constant__ dgs_chunk_desc indptr, const IdT* __r
   // the two round trips overlap; an entry past the count is never used
   const IdT seed_raw = i < nc.bound ? seeds[i] : IdT(0);
   const int64_t n = count_of(nc);
+  const int64_t s = static_cast<int64_t>(seed_raw);
+  const bool good = i < n && s >= 0 && s + 1 < indptr.total;
+  if (i < n && !good) raise_status(status, DGS_ERR_RANGE);
+  // indptr[s] and indptr[s + 1] are fetched by TWO NEIGHBOURING LANES in one load instruction, half a warp's
+  // seeds at a time: the two addresses (almost always) lie in the same 128-byte line, so the pair costs one
+  // memory request instead of the two that two loads of one thread cost.  Inside one GPU that is noise; when
+  // the row of indptr lives on a peer, requests are what the link can deliver only so many of per second.
+  const int lane = threadIdx.x & 31;
+  int64_t pair[2] = {0, 0};  // this lane's (row begin, row end) after the two half-warp passes
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int owner = half * 16 + (lane >> 1);  // the lane whose seed this lane fetches an element for
+    const int64_t so = __shfl_sync(FULL_MASK, s, owner);
+    const bool ok = __shfl_sync(FULL_MASK, good ? 1 : 0, owner) != 0;
+    const int64_t v = ok ? static_cast<int64_t>(load_at<IdT>(indptr, sh, so + (lane & 1))) : 0;
+    const int64_t lo = __shfl_sync(FULL_MASK, v, 2 * (lane & 15));
+    const int64_t hi = __shfl_sync(FULL_MASK, v, 2 * (lane & 15) + 1);
+    if ((lane >> 4) == half) {
+      pair[0] = lo;
+      pair[1] = hi;
+    }
+  }
   int64_t cnt = 0;
   if (i < n) {
-    const int64_t s = static_cast<int64_t>(seed_raw);
     int64_t rb = 0, deg = 0;
-    if (s < 0 || s + 1 >= indptr.total) {
-      raise_status(status, DGS_ERR_RANGE);
-    } else {
-      int64_t run;
-      const IdT* p = reinterpret_cast<const IdT*>(resolve(indptr, sh, s, &run));
-      rb = static_cast<int64_t>(p[0]);
-      const int64_t re = run >= 2 ? static_cast<int64_t>(p[1]) : static_cast<int64_t>(load_at<IdT>(indptr, sh, s + 1));
-      deg = re - rb;
+    if (good) {
+      rb = pair[0];
+      deg = pair[1] - rb;
       if (deg < 0 || rb < 0) {
         raise_status(status, DGS_ERR_RANGE);
         deg = 0;
