@@ -67,15 +67,22 @@ __device__ __forceinline__ bool publish_and_scan_tiles(int64_t my_tile_sum, int6
   __syncthreads();
   if (!s_last) return false;
   __threadfence();
+  // Every thread takes a contiguous run of `per` tiles: all loads of the CTA are issued together (one round
+  // trip to L2 whatever the number of tiles, instead of one per BLOCK tiles), one block scan over the threads'
+  // sums gives each run its offset, and a second walk over the run (now in L1/L2) writes the prefixes.  This
+  // CTA works alone at the end of its kernel, so every microsecond here is latency of the whole sequence.
   const int64_t ntiles = n_tiles;
-  int64_t carry = 0;
-  for (int64_t t0 = 0; t0 < ntiles; t0 += BLOCK) {
-    const int64_t t = t0 + threadIdx.x;
-    const int64_t v = t < ntiles ? __ldcg(tile_sums + t) : 0;
-    int64_t sum;
-    const int64_t e = block_exclusive_scan<int64_t, BLOCK>(v, smem, &sum);
-    if (t < ntiles) tile_sums[t] = carry + e;
-    carry += sum;
+  const int64_t per = (ntiles + BLOCK - 1) / BLOCK;
+  const int64_t lo = static_cast<int64_t>(threadIdx.x) * per;
+  const int64_t hi = lo + per < ntiles ? lo + per : ntiles;
+  int64_t mine = 0;
+  for (int64_t t = lo; t < hi; ++t) mine += __ldcg(tile_sums + t);
+  int64_t carry;
+  int64_t run = block_exclusive_scan<int64_t, BLOCK>(mine, smem, &carry);
+  for (int64_t t = lo; t < hi; ++t) {
+    const int64_t v = __ldcg(tile_sums + t);
+    tile_sums[t] = run;
+    run += v;
   }
   if (threadIdx.x == 0) {
     if (total_dev != nullptr) *total_dev = carry;
