@@ -23,10 +23,24 @@
 // so far on the caller's current stream, so consumers that were launched there
 // before it are safe.
 //
+// The twenty driver calls that queue a batch (about 60-80 us of host time) are made
+// by a thread the pipeline owns: submit() only fixes what must happen on the
+// caller's thread (the ordering event on its stream, the random stream of the
+// batch) and hands the rest over, so the caller's thread -- in the reference's
+// setting the Python training loop -- is free again after a few microseconds.
+// next() waits for that thread to have queued the batch before it waits for the
+// batch's sizes.  Failures of the queuing calls are kept and thrown by next().
+//
 // No counterpart in src/pybind.cc: an addition like the _CAPI_sample_blocks*
 // operators, built from the same C ABI calls.
 #pragma once
 #include <ATen/cuda/CUDAGeneratorImpl.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <string>
+#include <thread>
 
 #include "chunk_tensor.h"
 
@@ -89,7 +103,7 @@ class BlockPipeline : public torch::CustomClassHolder {
 
     const auto dev = torch::Device(torch::kCUDA, static_cast<c10::DeviceIndex>(device_));
     const auto id_opt = torch::TensorOptions().dtype(indptr_->dtype()).device(dev);
-    slots_.resize(depth);
+    slots_ = std::vector<Slot>(static_cast<size_t>(depth));
     // The sampling sequence is a chain of short kernels with thousands of CTAs each; the feature gather is one
     // long kernel that, in its bulk-copy form, needs a single small CTA per SM for its whole duration and
     // keeps its bytes in flight in shared memory.  Each slot therefore gathers on a stream of its own with the
@@ -130,9 +144,19 @@ class BlockPipeline : public torch::CustomClassHolder {
     // the buffers were allocated on the current stream; nothing of theirs is pending there, but make the
     // slots' streams start after whatever the allocator's stream still holds
     TORCH_CHECK(cudaStreamSynchronize(current_stream()) == cudaSuccess, "BlockPipeline: synchronisation failed");
+    static const char* inline_env = std::getenv("DGS_PIPELINE_INLINE_SUBMIT");  // 1: queue on the caller's thread
+    if (!(inline_env != nullptr && inline_env[0] == '1')) worker_ = std::thread([this] { worker_loop(); });
   }
 
   ~BlockPipeline() override {
+    if (worker_.joinable()) {
+      {
+        std::lock_guard<std::mutex> lock(mu_);
+        stop_ = true;
+      }
+      cv_.notify_all();
+      worker_.join();
+    }
     for (Slot& s : slots_) {
       if (s.stream != nullptr) cudaStreamSynchronize(s.stream);
       if (s.gather_stream != nullptr) cudaStreamSynchronize(s.gather_stream);
@@ -146,8 +170,9 @@ class BlockPipeline : public torch::CustomClassHolder {
   }
 
   // Queue one mini-batch.  `seeds`: 1-D ids of the graph's id type, at most max_seeds of them, on the
-  // pipeline's device or in (preferably pinned) host memory; they are copied into the slot, so the caller
-  // may reuse its tensor as soon as this returns and the current stream has moved on.
+  // pipeline's device or in (preferably pinned) host memory; they are copied into the slot ON THE CALLER'S
+  // CURRENT STREAM, so whatever the caller does with its tensor afterwards on that stream (overwrite it,
+  // free it) is ordered behind the copy.
   void submit(torch::Tensor seeds) {
     TORCH_CHECK(in_flight_ < static_cast<int64_t>(slots_.size()),
                 "BlockPipeline.submit: all ", slots_.size(), " slots hold batches; call next() first");
@@ -162,46 +187,33 @@ class BlockPipeline : public torch::CustomClassHolder {
     report_late_status(s, "BlockPipeline.submit");
     s.n_seeds = n;
     s.batch = head_;
+    s.error.clear();
     if (n > 0) {
-      // everything the caller queued so far (the seeds' producer, consumers of this slot's previous
-      // results) comes first
-      cudaStream_t cur = current_stream();
-      TORCH_CHECK(cudaEventRecord(s.ready, cur) == cudaSuccess && cudaStreamWaitEvent(s.stream, s.ready, 0) == cudaSuccess,
-                  "BlockPipeline.submit: cannot order the slot's stream after the current stream");
+      // the seeds go into the slot on the caller's stream; then everything the caller queued so far (the
+      // seeds' producer, this copy, consumers of the slot's previous results) comes before the slot's own
+      // stream: the event is recorded here, on the caller's thread and stream
       const size_t esz = ids64_ ? 8 : 4;
       TORCH_CHECK(cudaMemcpyAsync(s.seeds.data_ptr(), seeds.data_ptr(), n * esz,
                                   seeds.device().is_cpu() ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice,
-                                  s.stream) == cudaSuccess,
+                                  current_stream()) == cudaSuccess,
                   "BlockPipeline.submit: copying the seeds failed: ", cudaGetErrorString(cudaGetLastError()));
-      dgs_hop hops[DGS_MAX_HOPS];
-      DGS_CHECK_RC(dgs_sample_blocks_bounds(n, applied_.data(), H_, indptr_->desc().total - 1, hops));
-      for (int h = 0; h < H_; ++h) {
-        hops[h].coo_row = s.rows[h].data_ptr();
-        hops[h].coo_col = s.cols[h].data_ptr();
-        hops[h].frontier = s.frontier[h].data_ptr();
-        s.edge_bound[h] = hops[h].seed_bound * hops[h].fanout;
-        s.frontier_bound[h] = hops[h].frontier_bound;
-        s.sizes[2 * h] = s.sizes[2 * h + 1] = kPending;
-      }
-      const auto rng = next_rng(static_cast<uint64_t>(H_));
-      DGS_CHECK_RC(dgs_sample_blocks(&indptr_->desc(), &indices_->desc(), probs_.defined() ? &probs_->desc() : nullptr,
-                                     s.seeds.data_ptr(), ids64_, hops, H_, replace_, rng.first, rng.second,
-                                     s.ws.data_ptr(), ws_bytes_, s.sizes, s.status, s.stream));
-      cudaStream_t last = s.stream;
-      if (features_.defined()) {
-        const int64_t* n_dev = dgs_sample_blocks_frontier_count(hops, H_, s.ws.data_ptr());
-        TORCH_CHECK(n_dev != nullptr, "BlockPipeline.submit: no frontier count");
-        if (s.gather_stream != nullptr) {
-          TORCH_CHECK(cudaEventRecord(s.sampled, s.stream) == cudaSuccess &&
-                          cudaStreamWaitEvent(s.gather_stream, s.sampled, 0) == cudaSuccess,
-                      "BlockPipeline.submit: cannot order the gather after the sampling sequence");
-          last = s.gather_stream;
+      TORCH_CHECK(cudaEventRecord(s.ready, current_stream()) == cudaSuccess,
+                  "BlockPipeline.submit: cannot record an event on the current stream");
+      for (int h = 0; h < H_; ++h) s.sizes[2 * h] = s.sizes[2 * h + 1] = kPending;
+      Job job;
+      job.slot = static_cast<int>(head_ % slots_.size());
+      job.rng = next_rng(static_cast<uint64_t>(H_));
+      if (worker_.joinable()) {
+        s.state.store(kQueuing, std::memory_order_release);
+        {
+          std::lock_guard<std::mutex> lock(mu_);
+          jobs_.push_back(std::move(job));
         }
-        DGS_CHECK_RC(dgs_gather_rows_counted(&features_->desc(), s.frontier[H_ - 1].data_ptr(), ids64_,
-                                             s.frontier_bound[H_ - 1], n_dev, features_->elem_stride(),
-                                             s.feats.data_ptr(), s.status, last));
+        cv_.notify_one();
+      } else {
+        queue_batch(job);
+        TORCH_CHECK(s.error.empty(), s.error);
       }
-      TORCH_CHECK(cudaEventRecord(s.done, last) == cudaSuccess, "BlockPipeline.submit: cannot record an event");
     }
     ++head_;
     ++in_flight_;
@@ -226,6 +238,17 @@ class BlockPipeline : public torch::CustomClassHolder {
       frontier = s.frontier[0].narrow(0, 0, 0);
       if (features_.defined()) feats = s.feats.narrow(0, 0, 0);
     } else {
+      // the submitting thread must have queued the batch (recorded `done`) before anything can wait for it
+      for (uint64_t spins = 1; s.state.load(std::memory_order_acquire) == kQueuing; ++spins) {
+        if ((spins & 0x3F) == 0) std::this_thread::yield();
+      }
+      if (!s.error.empty()) {
+        const std::string msg = s.error;
+        s.error.clear();
+        ++tail_;
+        --in_flight_;
+        TORCH_CHECK(false, msg);
+      }
       for (int h = 0; h < H_; ++h) {
         const int64_t nnz = wait_size(s.sizes + 2 * h, s.stream, "BlockPipeline.next");
         const int64_t nu = wait_size(s.sizes + 2 * h + 1, s.stream, "BlockPipeline.next");
@@ -264,8 +287,16 @@ class BlockPipeline : public torch::CustomClassHolder {
 
  private:
   static constexpr int64_t kBudgetBytes = int64_t(32) << 30;
+  static constexpr int kIdle = 0, kQueuing = 1;
+
+  struct Job {
+    int slot = 0;
+    std::pair<uint64_t, uint64_t> rng;
+  };
 
   struct Slot {
+    std::atomic<int> state{kIdle};  // kQueuing while the submitting thread still has the batch's launches to make
+    std::string error;              // what went wrong while queuing, thrown by next()
     cudaStream_t stream = nullptr;         // sampling sequence
     cudaStream_t gather_stream = nullptr;  // feature gather (higher priority); null: everything on `stream`
     cudaEvent_t ready = nullptr, sampled = nullptr, done = nullptr;
@@ -276,6 +307,61 @@ class BlockPipeline : public torch::CustomClassHolder {
     int64_t edge_bound[DGS_MAX_HOPS] = {0}, frontier_bound[DGS_MAX_HOPS] = {0};
     int64_t n_seeds = 0, batch = -1;
   };
+
+  void worker_loop() {
+    cudaSetDevice(device_);
+    for (;;) {
+      Job job;
+      {
+        std::unique_lock<std::mutex> lock(mu_);
+        cv_.wait(lock, [this] { return stop_ || !jobs_.empty(); });
+        if (jobs_.empty()) return;  // stop requested and nothing left to queue
+        job = std::move(jobs_.front());
+        jobs_.pop_front();
+      }
+      queue_batch(job);
+      slots_[job.slot].state.store(kIdle, std::memory_order_release);
+    }
+  }
+
+  // The driver calls of one batch; any failure ends up in the slot's `error`.
+  void queue_batch(const Job& job) {
+    Slot& s = slots_[job.slot];
+    try {
+      const int64_t n = s.n_seeds;
+      TORCH_CHECK(cudaStreamWaitEvent(s.stream, s.ready, 0) == cudaSuccess,
+                  "BlockPipeline: cannot order the slot's stream after the caller's stream");
+      dgs_hop hops[DGS_MAX_HOPS];
+      DGS_CHECK_RC(dgs_sample_blocks_bounds(n, applied_.data(), H_, indptr_->desc().total - 1, hops));
+      for (int h = 0; h < H_; ++h) {
+        hops[h].coo_row = s.rows[h].data_ptr();
+        hops[h].coo_col = s.cols[h].data_ptr();
+        hops[h].frontier = s.frontier[h].data_ptr();
+        s.edge_bound[h] = hops[h].seed_bound * hops[h].fanout;
+        s.frontier_bound[h] = hops[h].frontier_bound;
+      }
+      DGS_CHECK_RC(dgs_sample_blocks(&indptr_->desc(), &indices_->desc(), probs_.defined() ? &probs_->desc() : nullptr,
+                                     s.seeds.data_ptr(), ids64_, hops, H_, replace_, job.rng.first, job.rng.second,
+                                     s.ws.data_ptr(), ws_bytes_, s.sizes, s.status, s.stream));
+      cudaStream_t last = s.stream;
+      if (features_.defined()) {
+        const int64_t* n_dev = dgs_sample_blocks_frontier_count(hops, H_, s.ws.data_ptr());
+        TORCH_CHECK(n_dev != nullptr, "BlockPipeline: no frontier count");
+        if (s.gather_stream != nullptr) {
+          TORCH_CHECK(cudaEventRecord(s.sampled, s.stream) == cudaSuccess &&
+                          cudaStreamWaitEvent(s.gather_stream, s.sampled, 0) == cudaSuccess,
+                      "BlockPipeline: cannot order the gather after the sampling sequence");
+          last = s.gather_stream;
+        }
+        DGS_CHECK_RC(dgs_gather_rows_counted(&features_->desc(), s.frontier[H_ - 1].data_ptr(), ids64_,
+                                             s.frontier_bound[H_ - 1], n_dev, features_->elem_stride(),
+                                             s.feats.data_ptr(), s.status, last));
+      }
+      TORCH_CHECK(cudaEventRecord(s.done, last) == cudaSuccess, "BlockPipeline: cannot record an event");
+    } catch (const std::exception& e) {
+      s.error = std::string("dgs: BlockPipeline batch ") + std::to_string(s.batch) + ": " + e.what();
+    }
+  }
 
   // a status left by kernels that were still running when next() handed the batch out
   static void report_late_status(Slot& s, const char* where) {
@@ -297,6 +383,12 @@ class BlockPipeline : public torch::CustomClassHolder {
   int64_t edge_cap_[DGS_MAX_HOPS] = {0}, frontier_cap_[DGS_MAX_HOPS] = {0};
   std::vector<Slot> slots_;
   int64_t head_ = 0, tail_ = 0, in_flight_ = 0;
+  // the submitting thread and its queue
+  std::thread worker_;
+  std::mutex mu_;
+  std::condition_variable cv_;
+  std::deque<Job> jobs_;
+  bool stop_ = false;
 };
 
 }  // namespace dgs

@@ -112,33 +112,35 @@ relabel_insert_kernel(const __grid_constant__ Keys keys, const TableSize size, S
     slot_of[i] = NO_SLOT;
     return;
   }
-  uint64_t h = hash_key(key) & mask;
   uint32_t found = NO_SLOT;
   if (size.compact) {
     unsigned long long* words = reinterpret_cast<unsigned long long*>(slots);
-    const unsigned long long mine = (static_cast<unsigned long long>(key) << 32) | static_cast<unsigned long long>(i);
-    for (uint64_t probes = 0; probes <= mask; ++probes) {
+    const uint32_t mask32 = static_cast<uint32_t>(mask), key32 = static_cast<uint32_t>(key);
+    const unsigned long long mine = (static_cast<unsigned long long>(key32) << 32) | static_cast<unsigned long long>(i);
+    uint32_t h = hash_key32(key32) & mask32;
+    for (uint32_t probes = 0; probes <= mask32; ++probes) {
       unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&words[h]);
       if (cur == EMPTY_COMPACT) {
         cur = atomicCAS(&words[h], EMPTY_COMPACT, mine);
         if (cur == EMPTY_COMPACT) {  // claimed, and the first index is in place: nothing else to do
-          found = static_cast<uint32_t>(h);
+          found = h;
           break;
         }
       }
-      if (static_cast<long long>(cur >> 32) == key) {
-        found = static_cast<uint32_t>(h);
+      if (static_cast<uint32_t>(cur >> 32) == key32) {
+        found = h;
         // same high half, so the minimum of the words is the minimum of the indices; a stale read can only
         // cause a redundant atomic (indices only ever decrease)
         if (static_cast<uint32_t>(cur) > static_cast<uint32_t>(i)) atomicMin(&words[h], mine);
         break;
       }
-      h = (h + 1) & mask;
+      h = (h + 1) & mask32;
     }
     slot_of[i] = found;
     if (found == NO_SLOT) raise_status(status, DGS_ERR_TABLE_FULL);
     return;
   }
+  uint64_t h = hash_key(key) & mask;
   for (uint64_t probes = 0; probes <= mask; ++probes) {
     long long cur = *reinterpret_cast<volatile long long*>(&slots[h].key);
     if (cur == EMPTY_KEY)
