@@ -21,6 +21,7 @@
 //     reported through the status word instead of faulting.
 //   * peer chunks (cudaIpc-mapped, NVLink) and the host tail (pinned, UVA) are
 //     ordinary global addresses, read with the same ld.global.nc vector loads.
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -561,21 +562,27 @@ int launch_gather_bulk(const Src& rows, Count nc, int64_t D, int sh, void* out, 
   constexpr int warps = BULK_WARPS;
   const size_t smem = static_cast<size_t>(warps) * BULK_STAGES * stage_bytes + warps * BULK_STAGES * sizeof(uint64_t);
   DGS_REQUIRE(smem <= 200 * 1024, DGS_ERR_UNSUPPORTED, "gather: %zu bytes of shared memory per CTA", smem);
-  static int sms = 0;
+  // per device and safe to reach from several host threads: the SM count, and whether this instantiation has
+  // been allowed its dynamic shared memory there (the attribute belongs to the device's copy of the kernel)
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> sm_count[kMaxDevices] = {};
+  static std::atomic<bool> smem_opted_in[kMaxDevices] = {};
+  int dev = 0;
+  DGS_CUDA_TRY(cudaGetDevice(&dev));
+  DGS_REQUIRE(dev >= 0 && dev < kMaxDevices, DGS_ERR_UNSUPPORTED, "gather: device ordinal %d", dev);
+  int sms = sm_count[dev].load(std::memory_order_relaxed);
   if (sms == 0) {
-    int dev = 0;
-    DGS_CUDA_TRY(cudaGetDevice(&dev));
     DGS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    sm_count[dev].store(sms, std::memory_order_relaxed);
   }
   // one persistent CTA per SM (two per SM: 0.70 instead of 0.68 alone, but the pipelined step got slower)
   const int64_t groups = (nc.bound + group - 1) / group;
   int64_t grid = (groups + warps - 1) / warps;
   if (grid > static_cast<int64_t>(sms)) grid = static_cast<int64_t>(sms);
   auto kernel = gather_rows_bulk_kernel<Src>;
-  static bool smem_opted_in = false;  // per instantiation; the buffers never exceed 12 x 8 KB + the barriers
-  if (!smem_opted_in) {
+  if (!smem_opted_in[dev].load(std::memory_order_acquire)) {  // the buffers never exceed 12 x 8 KB + the barriers
     DGS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    smem_opted_in = true;
+    smem_opted_in[dev].store(true, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
