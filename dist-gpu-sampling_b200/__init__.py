@@ -119,6 +119,10 @@ ABI_SIGNATURES = {
     "dgs_sample_blocks": (ctypes.c_int, [_DP, _DP, _DP, _VP, _I32, _HP, _I32, _I32, _U64, _U64, _VP, _SZ, _VP, _VP,
                                          _VP]),
     "dgs_sample_blocks_frontier_count": (_VP, [_HP, _I32, _VP]),
+    "dgs_sample_blocks_record": (ctypes.c_int, [_DP, _DP, _DP, _VP, _I32, _HP, _I32, _I32, _VP, _VP, _SZ, _VP, _VP,
+                                                _VP, ctypes.POINTER(_VP)]),
+    "dgs_sample_blocks_replay": (ctypes.c_int, [_VP, _VP]),
+    "dgs_sample_blocks_recording_free": (None, [_VP]),
     "dgs_cache_table_slots": (_I64, [_I64]),
     "dgs_cache_build": (ctypes.c_int, [_VP, _VP, _I32, _I64, _VP, _VP, _I64, _VP, _VP]),
     "dgs_cache_fetch": (ctypes.c_int, [_VP, _I64, _DP, _VP, _I32, _I64, _I64, _VP, _VP, _I64, _VP, _VP, _VP]),

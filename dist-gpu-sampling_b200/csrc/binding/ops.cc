@@ -484,6 +484,7 @@ TORCH_LIBRARY(dgs_classes, m) {
       .def("submit", &BlockPipeline::submit)
       .def("next", &BlockPipeline::next)
       .def("pending", &BlockPipeline::pending)
+      .def("recorded_slots", &BlockPipeline::recorded_slots)
       .def("depth", &BlockPipeline::depth);
 }
 

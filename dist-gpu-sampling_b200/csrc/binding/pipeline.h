@@ -30,6 +30,11 @@
 // setting the Python training loop -- is free again after a few microseconds.
 // next() waits for that thread to have queued the batch before it waits for the
 // batch's sizes.  Failures of the queuing calls are kept and thrown by next().
+// The launches of the sampling sequence are the same for every batch of a slot
+// that has the same number of seeds, so a slot records them once
+// (dgs_sample_blocks_record) and later batches replay the recording with one
+// call; the random stream of a batch travels through two pinned words.
+// DGS_PIPELINE_RECORD=0 keeps every batch on individual launches.
 //
 // No counterpart in src/pybind.cc: an addition like the _CAPI_sample_blocks*
 // operators, built from the same C ABI calls.
@@ -130,6 +135,7 @@ class BlockPipeline : public torch::CustomClassHolder {
       std::memset(p, 0, 256);
       s.sizes = static_cast<int64_t*>(p);
       s.status = reinterpret_cast<int32_t*>(static_cast<char*>(p) + 2 * DGS_MAX_HOPS * sizeof(int64_t));
+      s.rng_words = reinterpret_cast<uint64_t*>(static_cast<char*>(p) + 192);
       s.seeds = torch::empty({max_seeds_}, id_opt);
       s.ws = byte_scratch(ws_bytes_, dev);
       for (int h = 0; h < H_; ++h) {
@@ -144,6 +150,8 @@ class BlockPipeline : public torch::CustomClassHolder {
     // the buffers were allocated on the current stream; nothing of theirs is pending there, but make the
     // slots' streams start after whatever the allocator's stream still holds
     TORCH_CHECK(cudaStreamSynchronize(current_stream()) == cudaSuccess, "BlockPipeline: synchronisation failed");
+    static const char* record_env = std::getenv("DGS_PIPELINE_RECORD");
+    record_ = !(record_env != nullptr && record_env[0] == '0');
     static const char* inline_env = std::getenv("DGS_PIPELINE_INLINE_SUBMIT");  // 1: queue on the caller's thread
     if (!(inline_env != nullptr && inline_env[0] == '1')) worker_ = std::thread([this] { worker_loop(); });
   }
@@ -160,6 +168,7 @@ class BlockPipeline : public torch::CustomClassHolder {
     for (Slot& s : slots_) {
       if (s.stream != nullptr) cudaStreamSynchronize(s.stream);
       if (s.gather_stream != nullptr) cudaStreamSynchronize(s.gather_stream);
+      dgs_sample_blocks_recording_free(s.recording);
       if (s.ready != nullptr) cudaEventDestroy(s.ready);
       if (s.sampled != nullptr) cudaEventDestroy(s.sampled);
       if (s.done != nullptr) cudaEventDestroy(s.done);
@@ -283,6 +292,12 @@ class BlockPipeline : public torch::CustomClassHolder {
   }
 
   int64_t pending() const { return in_flight_; }
+  // slots whose sampling sequence is currently held as a recording (call with nothing in flight)
+  int64_t recorded_slots() const {
+    int64_t n = 0;
+    for (const Slot& s : slots_) n += s.recording != nullptr ? 1 : 0;
+    return n;
+  }
   int64_t depth() const { return static_cast<int64_t>(slots_.size()); }
 
  private:
@@ -302,6 +317,9 @@ class BlockPipeline : public torch::CustomClassHolder {
     cudaEvent_t ready = nullptr, sampled = nullptr, done = nullptr;
     int64_t* sizes = nullptr;   // [2 * DGS_MAX_HOPS], pinned
     int32_t* status = nullptr;  // pinned
+    uint64_t* rng_words = nullptr;  // pinned (seed, offset) of the batch, read by a replayed recording
+    dgs_blocks_recording* recording = nullptr;  // the sampling sequence for `recorded_seeds` seeds
+    int64_t recorded_seeds = -1, odd_seeds = -1;
     torch::Tensor seeds, ws, feats;
     std::vector<torch::Tensor> rows, cols, frontier;  // indexed by hop of application
     int64_t edge_bound[DGS_MAX_HOPS] = {0}, frontier_bound[DGS_MAX_HOPS] = {0};
@@ -340,9 +358,34 @@ class BlockPipeline : public torch::CustomClassHolder {
         s.edge_bound[h] = hops[h].seed_bound * hops[h].fanout;
         s.frontier_bound[h] = hops[h].frontier_bound;
       }
-      DGS_CHECK_RC(dgs_sample_blocks(&indptr_->desc(), &indices_->desc(), probs_.defined() ? &probs_->desc() : nullptr,
-                                     s.seeds.data_ptr(), ids64_, hops, H_, replace_, job.rng.first, job.rng.second,
-                                     s.ws.data_ptr(), ws_bytes_, s.sizes, s.status, s.stream));
+      const dgs_chunk_desc* probs = probs_.defined() ? &probs_->desc() : nullptr;
+      if (record_ && s.recorded_seeds != n && (s.recording == nullptr || s.odd_seeds == n)) {
+        // first batch of the slot, or a new batch size seen twice in a row: record the sequence for it
+        dgs_sample_blocks_recording_free(s.recording);
+        s.recording = nullptr;
+        s.recorded_seeds = -1;
+        const int rc = dgs_sample_blocks_record(&indptr_->desc(), &indices_->desc(), probs, s.seeds.data_ptr(), ids64_,
+                                                hops, H_, replace_, s.rng_words, s.ws.data_ptr(), ws_bytes_, s.sizes,
+                                                s.status, s.stream, &s.recording);
+        if (rc == DGS_OK) {
+          s.recorded_seeds = n;
+        } else {
+          // recording is an optimisation: say so once and go on with individual launches
+          record_ = false;
+          TORCH_WARN("dgs: BlockPipeline could not record its launch sequence (", dgs_last_error(),
+                     "); batches are queued launch by launch");
+        }
+      }
+      s.odd_seeds = (s.recorded_seeds == n) ? -1 : n;
+      if (s.recording != nullptr && s.recorded_seeds == n) {
+        s.rng_words[0] = job.rng.first;
+        s.rng_words[1] = job.rng.second;
+        DGS_CHECK_RC(dgs_sample_blocks_replay(s.recording, s.stream));
+      } else {
+        DGS_CHECK_RC(dgs_sample_blocks(&indptr_->desc(), &indices_->desc(), probs, s.seeds.data_ptr(), ids64_, hops, H_,
+                                       replace_, job.rng.first, job.rng.second, s.ws.data_ptr(), ws_bytes_, s.sizes,
+                                       s.status, s.stream));
+      }
       cudaStream_t last = s.stream;
       if (features_.defined()) {
         const int64_t* n_dev = dgs_sample_blocks_frontier_count(hops, H_, s.ws.data_ptr());
@@ -375,7 +418,7 @@ class BlockPipeline : public torch::CustomClassHolder {
 
   c10::intrusive_ptr<ChunkTensor> indptr_, indices_, probs_, features_;
   std::vector<int64_t> applied_;
-  bool replace_ = false, ids64_ = true;
+  bool replace_ = false, ids64_ = true, record_ = true;
   int H_ = 0;
   int device_ = 0;
   int64_t max_seeds_ = 0;

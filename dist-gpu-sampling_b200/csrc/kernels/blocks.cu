@@ -22,9 +22,11 @@
 // so a seed's relabelled id is its position and the sampler writes that directly;
 // only the first hop (whose seeds the caller may repeat) looks its rows up.
 #include <cstdlib>
+#include <new>
 
 #include "common.cuh"
 #include "launchers.h"
+#include "philox.cuh"
 
 namespace dgs {
 namespace {
@@ -37,12 +39,21 @@ struct InitWords {
   int64_t n0_value;
   int n_tickets;
   unsigned int* tickets[2 * DGS_MAX_HOPS];
+  // a recorded sequence takes its random stream from memory: (seed, offset) at rng_src, read by this
+  // kernel on every replay and folded into one Philox key per hop for the sampling kernels behind it
+  const uint64_t* rng_src;
+  uint64_t* keys;
+  int n_keys;
 };
 
 __global__ void blocks_init_kernel(const InitWords w) {
   pdl_enter();
   if (threadIdx.x == 0) *w.n0 = w.n0_value;
   if (threadIdx.x < w.n_tickets) *w.tickets[threadIdx.x] = 0u;
+  if (w.rng_src != nullptr && threadIdx.x < w.n_keys) {
+    const volatile uint64_t* src = w.rng_src;  // host-written words: no cached copy
+    w.keys[threadIdx.x] = fold_rng_key(src[0], src[1] + static_cast<uint64_t>(threadIdx.x));
+  }
 }
 
 __global__ void zero_sizes_kernel(int64_t* sizes, int n) {
@@ -115,12 +126,15 @@ extern "C" const int64_t* dgs_sample_blocks_frontier_count(const dgs_hop* hops, 
   return nullptr;
 }
 
-extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_desc* indices,
-                                 const dgs_chunk_desc* probs, const void* seeds, int32_t ids64,
-                                 const dgs_hop* hops, int32_t n_hops, int32_t replace, uint64_t rng_seed,
-                                 uint64_t rng_offset, void* workspace, size_t workspace_bytes,
-                                 int64_t* sizes, int32_t* status, dgs_stream_t stream) {
-  using namespace dgs;
+namespace dgs {
+namespace {
+
+// Queues the whole sequence on `stream`.  rng_words == nullptr: the keys come from (rng_seed, rng_offset) as
+// launch parameters; otherwise the first kernel reads (seed, offset) from rng_words when it RUNS.
+int queue_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_desc* indices, const dgs_chunk_desc* probs,
+                 const void* seeds, int32_t ids64, const dgs_hop* hops, int32_t n_hops, int32_t replace,
+                 uint64_t rng_seed, uint64_t rng_offset, const uint64_t* rng_words, void* workspace,
+                 size_t workspace_bytes, int64_t* sizes, int32_t* status, dgs_stream_t stream) {
   int rc = validate_desc(indptr, "dgs_sample_blocks(indptr)");
   if (rc != DGS_OK) return rc;
   rc = validate_desc(indices, "dgs_sample_blocks(indices)");
@@ -161,7 +175,9 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
   p += WS_ALIGN;
   void* plan[DGS_MAX_HOPS];
   void* table[DGS_MAX_HOPS];
-  InitWords init{n0_dev, n0, 0, {}};
+  static_assert(sizeof(int64_t) * (1 + DGS_MAX_HOPS) <= WS_ALIGN, "the control words hold n0 and one key per hop");
+  uint64_t* keys_dev = reinterpret_cast<uint64_t*>(n0_dev + 1);
+  InitWords init{n0_dev, n0, 0, {}, rng_words, keys_dev, n_hops};
   for (int h = 0; h < n_hops; ++h) {
     const int64_t key_bound = hops[h].seed_bound * (1 + hops[h].fanout);
     plan[h] = p;
@@ -199,7 +215,9 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
                             make_clear_job(table[h], key_bound, size), pending, status, s);
     if (rc != DGS_OK) return rc;
     const int64_t* nnz_dev = sample_plan_total(plan[h], hp.seed_bound);
-    const uint64_t key = sample_rng_key(rng_seed, rng_offset + static_cast<uint64_t>(h));
+    const RngKey key = rng_words != nullptr
+                           ? RngKey{0, keys_dev + h}
+                           : host_key(sample_rng_key(rng_seed, rng_offset + static_cast<uint64_t>(h)));
     const bool row_is_position = h > 0;
     rc = probs != nullptr
              ? launch_sample_weighted(*indices, *probs, hop_seeds, ids64 != 0, n, k, replace != 0, plan[h],
@@ -220,4 +238,76 @@ extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_d
     n_dev = unique_total(table[h], key_bound);
   }
   return launch_lookup(pending, ids64 != 0, s);
+}
+
+}  // namespace
+}  // namespace dgs
+
+extern "C" int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_desc* indices,
+                                 const dgs_chunk_desc* probs, const void* seeds, int32_t ids64,
+                                 const dgs_hop* hops, int32_t n_hops, int32_t replace, uint64_t rng_seed,
+                                 uint64_t rng_offset, void* workspace, size_t workspace_bytes,
+                                 int64_t* sizes, int32_t* status, dgs_stream_t stream) {
+  return dgs::queue_blocks(indptr, indices, probs, seeds, ids64, hops, n_hops, replace, rng_seed, rng_offset, nullptr,
+                           workspace, workspace_bytes, sizes, status, stream);
+}
+
+// ---- the sequence recorded once and replayed ------------------------------------
+// Queuing a batch is ~18 kernel launches with the same parameters every time as long as the buffers, the
+// bounds (the number of seeds) and the tables stay the same; only the random stream differs.  A recording
+// holds those launches as one executable graph (stream capture keeps the programmatic edges between the
+// kernels), and a replay is a single launch call.
+struct dgs_blocks_recording {
+  cudaGraphExec_t exec = nullptr;
+};
+
+extern "C" int dgs_sample_blocks_record(const dgs_chunk_desc* indptr, const dgs_chunk_desc* indices,
+                                        const dgs_chunk_desc* probs, const void* seeds, int32_t ids64,
+                                        const dgs_hop* hops, int32_t n_hops, int32_t replace,
+                                        const uint64_t* rng_words, void* workspace, size_t workspace_bytes,
+                                        int64_t* sizes, int32_t* status, dgs_stream_t capture_stream,
+                                        dgs_blocks_recording** out) {
+  using namespace dgs;
+  DGS_REQUIRE(out != nullptr && rng_words != nullptr, DGS_ERR_INVALID, "dgs_sample_blocks_record: null argument");
+  DGS_REQUIRE(capture_stream != nullptr, DGS_ERR_INVALID,
+              "dgs_sample_blocks_record: the default stream cannot record; pass a stream of your own");
+  *out = nullptr;
+  cudaStream_t s = static_cast<cudaStream_t>(capture_stream);
+  // thread-local mode: other host threads keep allocating and copying while this one records
+  DGS_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+  const int rc = queue_blocks(indptr, indices, probs, seeds, ids64, hops, n_hops, replace, 0, 0, rng_words, workspace,
+                              workspace_bytes, sizes, status, capture_stream);
+  cudaGraph_t graph = nullptr;
+  const cudaError_t end = cudaStreamEndCapture(s, &graph);  // always closed, also after a refused argument
+  if (rc != DGS_OK) {
+    if (graph != nullptr) cudaGraphDestroy(graph);
+    (void)cudaGetLastError();
+    return rc;
+  }
+  if (end != cudaSuccess) return cuda_fail(end, "cudaStreamEndCapture", __FILE__, __LINE__);
+  cudaGraphExec_t exec = nullptr;
+  const cudaError_t inst = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (inst != cudaSuccess) return cuda_fail(inst, "cudaGraphInstantiate", __FILE__, __LINE__);
+  dgs_blocks_recording* rec = new (std::nothrow) dgs_blocks_recording;
+  if (rec == nullptr) {
+    cudaGraphExecDestroy(exec);
+    DGS_REQUIRE(false, DGS_ERR_CUDA, "dgs_sample_blocks_record: out of host memory");
+  }
+  rec->exec = exec;
+  *out = rec;
+  return DGS_OK;
+}
+
+extern "C" int dgs_sample_blocks_replay(dgs_blocks_recording* rec, dgs_stream_t stream) {
+  using namespace dgs;
+  DGS_REQUIRE(rec != nullptr && rec->exec != nullptr, DGS_ERR_INVALID, "dgs_sample_blocks_replay: null recording");
+  DGS_CUDA_TRY(cudaGraphLaunch(rec->exec, static_cast<cudaStream_t>(stream)));
+  return DGS_OK;
+}
+
+extern "C" void dgs_sample_blocks_recording_free(dgs_blocks_recording* rec) {
+  if (rec == nullptr) return;
+  if (rec->exec != nullptr) cudaGraphExecDestroy(rec->exec);
+  delete rec;
 }

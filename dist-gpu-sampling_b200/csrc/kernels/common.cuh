@@ -56,6 +56,15 @@ struct Count {
 };
 static inline Count exact_count(int64_t n) { return Count{n, nullptr, nullptr}; }
 
+// The Philox key of one sampling launch: a value the host computed, or (dev != nullptr) a device word an
+// earlier kernel of the same stream wrote -- what a recorded launch sequence needs, whose parameters are
+// fixed while its random stream changes from replay to replay.
+struct RngKey {
+  uint64_t value;
+  const uint64_t* dev;
+};
+static inline RngKey host_key(uint64_t v) { return RngKey{v, nullptr}; }
+
 #ifdef __CUDACC__
 
 constexpr unsigned FULL_MASK = 0xffffffffu;
@@ -99,6 +108,8 @@ __device__ __forceinline__ int64_t count_of(const Count& c) {
   if (c.dev2 != nullptr) v += *c.dev2;
   return v < c.bound ? (v < 0 ? 0 : v) : c.bound;
 }
+
+__device__ __forceinline__ uint64_t key_of(const RngKey& k) { return k.dev == nullptr ? k.value : *k.dev; }
 
 // Sticky status word: first error wins, later ones are dropped.
 __device__ __forceinline__ void raise_status(int32_t* status, int32_t code) {

@@ -23,12 +23,12 @@ unsigned int* sample_plan_ticket(void* plan, int64_t n_bound);
 // row_is_position: write the seed's position in the seed list to coo_row instead
 // of the seed id (valid as a relabelled id when the seed list has no duplicates).
 int launch_sample_uniform(const dgs_chunk_desc& indices, const void* seeds, bool ids64, Count n, int64_t k,
-                          bool replace, void* plan, uint64_t key, void* coo_row,
+                          bool replace, void* plan, RngKey key, void* coo_row,
                           void* coo_col, int64_t out_capacity, int64_t* picked_pos, bool row_is_position,
                           int32_t* status, cudaStream_t s);
 int launch_sample_weighted(const dgs_chunk_desc& indices, const dgs_chunk_desc& probs, const void* seeds,
                            bool ids64, Count n, int64_t k, bool replace, void* plan,
-                           uint64_t key, void* coo_row, void* coo_col, int64_t out_capacity,
+                           RngKey key, void* coo_row, void* coo_col, int64_t out_capacity,
                            int64_t* picked_pos, bool row_is_position, int32_t* status, cudaStream_t s);
 uint64_t sample_rng_key(uint64_t rng_seed, uint64_t rng_offset);
 

@@ -54,6 +54,12 @@ DGS_HD uint64_t mix64(uint64_t z) {
   return z ^ (z >> 31);
 }
 
+// (seed, offset) of a random stream folded into the Philox key of one sampling launch; the same on the
+// host (launch parameter) and on the device (a recorded sequence reads seed and offset when it runs).
+DGS_HD uint64_t fold_rng_key(uint64_t rng_seed, uint64_t rng_offset) {
+  return mix64(rng_seed) ^ mix64(rng_offset ^ 0xA5A5A5A55A5A5A5Aull);
+}
+
 // Unbiased integer in [0, n), n >= 1, from one Philox block (Lemire's
 // multiply-shift with rejection; the reference's `curand() % n` is biased).
 // The four 32-bit words are four successive attempts; a fifth rejection has

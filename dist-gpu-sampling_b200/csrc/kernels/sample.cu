@@ -214,11 +214,12 @@ sample_uniform_kernel(const __grid_constant__ dgs_chunk_desc indices, const IdT*
                       const Count nc, const int64_t k, const bool replace,
                       const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
                       const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
-                      const uint64_t key, IdT* coo_row, IdT* coo_col,
+                      const RngKey rng, IdT* coo_row, IdT* coo_col,
                       const int64_t out_capacity, int64_t* __restrict__ picked_pos,
                       const bool row_is_position, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
   pdl_enter();
+  const uint64_t key = key_of(rng);
   constexpr int GROUPS = SAMPLE_BLOCK / G;  // seeds per CTA
   constexpr int TAKEN_WORDS = 4096;         // 16 KB of position bitmaps per CTA, split between its groups
   __shared__ uint32_t s_taken[TAKEN_WORDS];
@@ -450,11 +451,12 @@ sample_weighted_kernel(const __grid_constant__ dgs_chunk_desc indices,
                        const Count nc, const int64_t k, const bool replace,
                        const int64_t* __restrict__ plan_rb, const int64_t* __restrict__ plan_deg,
                        const int64_t* __restrict__ local_off, const int64_t* __restrict__ tile_off,
-                       const uint64_t key, IdT* coo_row, IdT* coo_col,
+                       const RngKey rng, IdT* coo_row, IdT* coo_col,
                        const int64_t out_capacity, int64_t* __restrict__ picked_pos,
                        const bool row_is_position, int32_t* __restrict__ status) {
   const Emit<IdT> emit{indices, coo_row, coo_col, picked_pos, out_capacity, status};
   pdl_enter();
+  const uint64_t key = key_of(rng);
   const int64_t n = count_of(nc);
   const int l = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -602,7 +604,7 @@ int plan_typed(const dgs_chunk_desc& indptr, const void* seeds, Count n, int64_t
 
 template <typename IdT>
 int uniform_typed(const dgs_chunk_desc& indices, const void* seeds, Count n, int64_t k, bool replace,
-                  const PlanView& pv, uint64_t key, void* coo_row, void* coo_col,
+                  const PlanView& pv, RngKey key, void* coo_row, void* coo_col,
                   int64_t cap, int64_t* pos, bool rowpos, int32_t* status, cudaStream_t s) {
 #define DGS_LAUNCH_U(G)                                                                                      \
   DGS_CUDA_TRY(launch_chained(SITE_SAMPLE, sample_uniform_kernel<IdT, G>,                                                 \
@@ -620,7 +622,7 @@ int uniform_typed(const dgs_chunk_desc& indices, const void* seeds, Count n, int
 
 template <typename IdT>
 int weighted_typed(const dgs_chunk_desc& indices, const dgs_chunk_desc& probs, const void* seeds, Count n,
-                   int64_t k, bool replace, const PlanView& pv, uint64_t key,
+                   int64_t k, bool replace, const PlanView& pv, RngKey key,
                    void* coo_row, void* coo_col, int64_t cap, int64_t* pos, bool rowpos, int32_t* status,
                    cudaStream_t s) {
   const unsigned grid = static_cast<unsigned>((n.bound + SAMPLE_BLOCK / 32 - 1) / (SAMPLE_BLOCK / 32));
@@ -637,7 +639,7 @@ int64_t* sample_plan_total(void* plan, int64_t n_bound) { return plan_view(plan,
 unsigned int* sample_plan_ticket(void* plan, int64_t n_bound) { return plan_view(plan, n_bound).ticket; }
 
 uint64_t sample_rng_key(uint64_t rng_seed, uint64_t rng_offset) {
-  return mix64(rng_seed) ^ mix64(rng_offset ^ 0xA5A5A5A55A5A5A5Aull);
+  return fold_rng_key(rng_seed, rng_offset);
 }
 
 int launch_sample_plan(const dgs_chunk_desc& indptr, const void* seeds, bool ids64, Count n, int64_t k,
@@ -651,7 +653,7 @@ int launch_sample_plan(const dgs_chunk_desc& indptr, const void* seeds, bool ids
 }
 
 int launch_sample_uniform(const dgs_chunk_desc& indices, const void* seeds, bool ids64, Count n, int64_t k,
-                          bool replace, void* plan, uint64_t key, void* coo_row,
+                          bool replace, void* plan, RngKey key, void* coo_row,
                           void* coo_col, int64_t out_capacity, int64_t* picked_pos, bool row_is_position,
                           int32_t* status, cudaStream_t s) {
   const PlanView pv = plan_view(plan, n.bound);
@@ -663,7 +665,7 @@ int launch_sample_uniform(const dgs_chunk_desc& indices, const void* seeds, bool
 
 int launch_sample_weighted(const dgs_chunk_desc& indices, const dgs_chunk_desc& probs, const void* seeds,
                            bool ids64, Count n, int64_t k, bool replace, void* plan,
-                           uint64_t key, void* coo_row, void* coo_col, int64_t out_capacity,
+                           RngKey key, void* coo_row, void* coo_col, int64_t out_capacity,
                            int64_t* picked_pos, bool row_is_position, int32_t* status, cudaStream_t s) {
   const PlanView pv = plan_view(plan, n.bound);
   return ids64 ? weighted_typed<int64_t>(indices, probs, seeds, n, k, replace, pv, key, coo_row, coo_col,
@@ -725,7 +727,7 @@ extern "C" int dgs_sample_uniform(const dgs_chunk_desc* indices, const void* see
   DGS_REQUIRE(out_capacity == 0 || (coo_row != nullptr && coo_col != nullptr), DGS_ERR_INVALID,
               "dgs_sample_uniform: null output");
   rc = launch_sample_uniform(*indices, seeds, ids64 != 0, exact_count(n), k, replace != 0, const_cast<void*>(plan),
-                             sample_rng_key(rng_seed, rng_offset), coo_row, coo_col, out_capacity,
+                             host_key(sample_rng_key(rng_seed, rng_offset)), coo_row, coo_col, out_capacity,
                              picked_pos, false, status, s);
   if (rc != DGS_OK) return rc;
   if (nnz != nullptr) {
@@ -765,7 +767,7 @@ extern "C" int dgs_sample_weighted(const dgs_chunk_desc* indices, const dgs_chun
   DGS_REQUIRE(out_capacity == 0 || (coo_row != nullptr && coo_col != nullptr), DGS_ERR_INVALID,
               "dgs_sample_weighted: null output");
   rc = launch_sample_weighted(*indices, *probs, seeds, ids64 != 0, exact_count(n), k, replace != 0,
-                              const_cast<void*>(plan), sample_rng_key(rng_seed, rng_offset), coo_row,
+                              const_cast<void*>(plan), host_key(sample_rng_key(rng_seed, rng_offset)), coo_row,
                               coo_col, out_capacity, picked_pos, false, status, s);
   if (rc != DGS_OK) return rc;
   if (nnz != nullptr) {

@@ -315,6 +315,29 @@ DGS_API int dgs_sample_blocks(const dgs_chunk_desc* indptr, const dgs_chunk_desc
 DGS_API const int64_t* dgs_sample_blocks_frontier_count(const dgs_hop* hops, int32_t n_hops,
                                                         void* workspace);
 
+/* The same sequence recorded once and replayed: queuing a batch through
+ * dgs_sample_blocks costs about eighteen kernel launches whose parameters do not
+ * change while buffers, bounds (hence the number of seeds) and graph stay the same.
+ * dgs_sample_blocks_record captures them on `capture_stream` (a stream of the
+ * caller's own, not the default stream; nothing runs) into one executable graph;
+ * dgs_sample_blocks_replay queues that graph on a stream with a single call.
+ * What differs between replays comes from memory: the seeds (rewrite the `seeds`
+ * buffer) and the random stream, read by the first kernel of every replay from
+ * rng_words[0] (seed) and rng_words[1] (offset) -- device-readable memory the host
+ * can write, i.e. pinned; hop h uses (seed, offset + h) like dgs_sample_blocks, so
+ * a replay gives bit for bit what dgs_sample_blocks gives for the same words.
+ * One replay of a recording at a time (they share the workspace and outputs).
+ * The arguments are those of dgs_sample_blocks.  No counterpart in the reference. */
+typedef struct dgs_blocks_recording dgs_blocks_recording;
+DGS_API int dgs_sample_blocks_record(const dgs_chunk_desc* indptr, const dgs_chunk_desc* indices,
+                                     const dgs_chunk_desc* probs, const void* seeds, int32_t ids64,
+                                     const dgs_hop* hops, int32_t n_hops, int32_t replace,
+                                     const uint64_t* rng_words, void* workspace,
+                                     size_t workspace_bytes, int64_t* sizes, int32_t* status,
+                                     dgs_stream_t capture_stream, dgs_blocks_recording** out);
+DGS_API int dgs_sample_blocks_replay(dgs_blocks_recording* rec, dgs_stream_t stream);
+DGS_API void dgs_sample_blocks_recording_free(dgs_blocks_recording* rec);
+
 /* ---- PaGraph-style feature cache ---------------------------------------- */
 /* CreateHashMapTensorCUDA, src/cuda/pagraph.cu:94-124: open-addressing table
  * key -> value with capacity dgs_cache_table_slots(n); key_buf/value_buf hold

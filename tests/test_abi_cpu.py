@@ -258,3 +258,21 @@ def test_counted_gather_and_frontier_count_reject_bad_arguments_before_any_launc
     assert abi.dgs_sample_blocks_frontier_count(None, 3, base) is None
     assert abi.dgs_sample_blocks_frontier_count(hops, 0, base) is None
     assert abi.dgs_sample_blocks_frontier_count(hops, 3, None) is None
+
+
+def test_recording_entry_points_reject_bad_arguments_before_any_cuda_call(abi, pkg):
+    """dgs_sample_blocks_record refuses a missing out pointer, missing random words and the default stream
+    before it touches CUDA; replay of nothing is an error code, freeing nothing is a no-op."""
+    INVALID = 1
+    hops = (pkg.Hop * 2)()
+    rec = ctypes.c_void_p()
+    args = lambda words, stream, out: (None, None, None, 0x2000, 1, hops, 2, 0, words, 0x3000, 1 << 20, 0x4000, None,
+                                       stream, out)
+    assert abi.dgs_sample_blocks_record(*args(None, 0x1, ctypes.byref(rec))) == INVALID
+    assert abi.dgs_sample_blocks_record(*args(0x5000, 0x1, None)) == INVALID
+    assert abi.dgs_sample_blocks_record(*args(0x5000, None, ctypes.byref(rec))) == INVALID
+    assert b"default stream" in abi.dgs_last_error()
+    assert not rec.value
+    assert abi.dgs_sample_blocks_replay(None, None) == INVALID
+    abi.dgs_sample_blocks_recording_free(None)
+

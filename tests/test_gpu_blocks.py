@@ -270,3 +270,79 @@ def test_blocks_over_emulated_multi_gpu_chunks(oracle, pkg, weighted):
             n_dst = sz[2 * h + 1]
         total = check_hops(oracle, indptr, indices, seeds, fanouts, False, bufs[H - 1][2][:n_dst], blocks)
         assert total == sum(sz[0::2])
+
+
+@pytest.mark.parametrize("weighted", [False, True])
+def test_recorded_sequence_replays_bit_for_bit(oracle, pkg, weighted):
+    """dgs_sample_blocks_record / _replay: a replay gives exactly what dgs_sample_blocks gives for the same
+    (seed, offset), for every new pair written to the pinned words and every new seed list written to the
+    seeds buffer, without recording again."""
+    from gpu_util import plain_desc, vp
+    abi = pkg.load_abi()
+    rng = np.random.default_rng(23)
+    indptr, indices = graph(rng, 6000, 40, hubs=(0, 900))
+    probs = (rng.random(indices.size) + 0.05).astype(np.float32)
+    ip, ix, pr = to_dev(indptr), to_dev(indices), torch.from_numpy(probs).cuda()
+    d_ip, d_ix, d_pr = plain_desc(ip), plain_desc(ix), plain_desc(pr)
+    fanouts, n_seeds, H = [5, 10, 15], 300, 3
+    applied = (ctypes.c_int64 * H)(*reversed(fanouts))
+
+    def buffers():
+        hops = (pkg.Hop * H)()
+        pkg.check(abi.dgs_sample_blocks_bounds(n_seeds, applied, H, 6000, hops))
+        wsb = abi.dgs_sample_blocks_workspace_bytes(hops, H)
+        ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+        bufs = []
+        for h in range(H):
+            cap = hops[h].seed_bound * hops[h].fanout
+            r, c = torch.full((cap,), -7, device="cuda"), torch.full((cap,), -7, device="cuda")
+            fr = torch.full((hops[h].frontier_bound,), -7, device="cuda")
+            hops[h].coo_row, hops[h].coo_col, hops[h].frontier = vp(r), vp(c), vp(fr)
+            bufs.append((r, c, fr))
+        sizes = torch.zeros(2 * H, dtype=torch.int64).pin_memory()
+        status = torch.zeros(1, dtype=torch.int32).pin_memory()
+        return hops, wsb, ws, bufs, sizes, status
+
+    def snapshot(bufs, sizes):
+        sz = sizes.tolist()
+        return sz, [(b[0][:sz[2 * h]].clone(), b[1][:sz[2 * h]].clone(), b[2][:sz[2 * h + 1]].clone())
+                    for h, b in enumerate(bufs)]
+
+    seeds_dev = torch.empty(n_seeds, dtype=torch.int64, device="cuda")
+    rng_words = torch.zeros(2, dtype=torch.int64).pin_memory()
+    hops_r, wsb, ws_r, bufs_r, sizes_r, status_r = buffers()
+    hops_d, _, ws_d, bufs_d, sizes_d, status_d = buffers()
+    stream = torch.cuda.Stream()
+    rec = ctypes.c_void_p()
+    pkg.check(abi.dgs_sample_blocks_record(ctypes.byref(d_ip), ctypes.byref(d_ix), ctypes.byref(d_pr) if weighted else None,
+                                           vp(seeds_dev), 1, hops_r, H, 0, vp(rng_words), vp(ws_r), wsb, vp(sizes_r),
+                                           vp(status_r), ctypes.c_void_p(stream.cuda_stream), ctypes.byref(rec)))
+    assert rec.value
+    torch.cuda.synchronize()
+    assert bool((bufs_r[0][0] == -7).all())                      # recording ran nothing
+    try:
+        for trial, (seed, offset) in enumerate([(7, 0), (7, 4), (123456789, 1 << 40), (7, 0)]):
+            seeds = rng.permutation(6000)[:n_seeds]
+            seeds_dev.copy_(to_dev(seeds))
+            rng_words[0], rng_words[1] = seed, offset
+            torch.cuda.synchronize()
+            pkg.check(abi.dgs_sample_blocks_replay(rec, ctypes.c_void_p(stream.cuda_stream)))
+            pkg.check(abi.dgs_sample_blocks(ctypes.byref(d_ip), ctypes.byref(d_ix), ctypes.byref(d_pr) if weighted else None,
+                                            vp(seeds_dev), 1, hops_d, H, 0, seed, offset, vp(ws_d), wsb, vp(sizes_d),
+                                            vp(status_d), None))
+            torch.cuda.synchronize()
+            assert status_r.item() == 0 and status_d.item() == 0
+            sz_r, out_r = snapshot(bufs_r, sizes_r)
+            sz_d, out_d = snapshot(bufs_d, sizes_d)
+            assert sz_r == sz_d and sz_r[0] > 0
+            for (a, b, c), (x, y, z) in zip(out_r, out_d):
+                assert torch.equal(a, x) and torch.equal(b, y) and torch.equal(c, z)
+            if trial == 0:
+                blocks, n_dst = [], n_seeds
+                for h in range(H):
+                    blocks.insert(0, (out_r[h][0], out_r[h][1], sz_r[2 * h + 1], n_dst))
+                    n_dst = sz_r[2 * h + 1]
+                assert sum(sz_r[0::2]) == check_hops(oracle, indptr, indices, seeds, fanouts, False, out_r[H - 1][2],
+                                                     blocks)
+    finally:
+        abi.dgs_sample_blocks_recording_free(rec)

@@ -83,6 +83,30 @@ def test_pipeline_stochastic_batches_are_valid_and_results_outlive_later_submits
     del sampler
 
 
+@pytest.mark.parametrize("weighted", [False, True])
+def test_replayed_batches_equal_the_one_at_a_time_operator_bit_for_bit(ops, pkg, weighted):
+    """From a slot's second batch of the same size on, the sampling sequence is a replayed recording; under
+    the same torch seed it must give exactly what _CAPI_sample_blocks* gives launch by launch."""
+    rng = np.random.default_rng(29)
+    indptr, indices = graph(rng, 15000, 50, hubs=(0, 7, 900))
+    probs = (rng.random(indices.size) + 0.05).astype(np.float32)
+    c_ip, c_ix, c_pr = chunked(indptr), chunked(indices, 0.8), chunked(probs, 0.8)
+    fanouts = [10, 10, 5]
+    batches = [to_dev(rng.permutation(15000)[:n]) for n in (384, 384, 384, 384, 100, 100, 100, 384, 384)]
+    sampler = pkg.PipelinedSampler(c_ip, c_ix, fanouts, probs=c_pr if weighted else None, max_seeds=384, depth=2)
+    torch.manual_seed(31)
+    piped = [(f.clone(), [(r.clone(), c.clone(), a, b) for r, c, a, b in blocks], ne)
+             for f, blocks, ne, _ in sampler(batches)]
+    assert sampler.pipe.recorded_slots() == 2
+    torch.manual_seed(31)
+    for (f, blocks, ne), seeds in zip(piped, batches):
+        f2, blocks2, ne2 = pkg.sample_blocks(seeds, fanouts, c_ip, c_ix, probs=c_pr if weighted else None, fused=True)
+        assert ne == ne2 and ne > 0 and torch.equal(f, f2)
+        for (r, c, a, b), (r2, c2, a2, b2) in zip(blocks, blocks2):
+            assert (a, b) == (a2, b2) and torch.equal(r, r2) and torch.equal(c, c2)
+    del sampler
+
+
 @pytest.mark.parametrize("weighted,replace", [(True, False), (True, True), (False, True)])
 def test_pipeline_weighted_replace_and_without_features(ops, oracle, pkg, weighted, replace):
     rng = np.random.default_rng(23)
