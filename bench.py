@@ -723,6 +723,18 @@ def measure_workload(env, args, pkg, wl, steps, warmup, full):
         k_rows += kept[i % len(kept)].numel()
     torch.cuda.synchronize()
     res["kernel"] = {"ms": sum(kev[i].elapsed_time(kev[i + 1]) for i in range(n_k)), "launches": n_k, "rows": k_rows}
+    # the same launches in the form the pipeline queues per batch (row count on the device; bulk-copy kernel
+    # where the rows qualify)
+    counts = [torch.tensor([fr.numel()], dtype=torch.int64, device=dev) for fr in kept]
+    for i in range(3):
+        wl.c_feats._CAPI_index_counted(kept[i % len(kept)], counts[i % len(kept)])
+    kev[0].record()
+    for i in range(n_k):
+        wl.c_feats._CAPI_index_counted(kept[i % len(kept)], counts[i % len(kept)])
+        kev[i + 1].record()
+    torch.cuda.synchronize()
+    res["kernel_counted"] = {"ms": sum(kev[i].elapsed_time(kev[i + 1]) for i in range(n_k)), "launches": n_k,
+                             "rows": k_rows}
     cls = [0, 0, 0]
     for fr in kept:
         for j, part in enumerate(wl.c_feats._CAPI_split_index(fr)):
@@ -790,7 +802,16 @@ def roofline_dict(res, w, peaks, hbm_peak, hbm_kind):
     peak = {"hbm": hbm_peak, "nvlink": nvl_peak, "host": host_peak}[bound]
     achieved = bytes_of / (ms * 1e-3) / 1e9
     per_row = NCU_TRAFFIC_BYTES_PER_ROW.get(dim)
-    return {"kernel": "gather_rows_kernel (features._CAPI_index)", "bound": bound,
+    kc = res.get("kernel_counted")
+    ms_counted = kc["ms"] / kc["launches"] if kc else None
+    return {"kernel": "gather_rows_kernel (features._CAPI_index; the register form, used by the one-batch-at-a-time "
+                      "APIs)", "bound": bound,
+            "pipeline_form": None if ms_counted is None else {
+                "kernel": "gather_rows_bulk_kernel where rows are 16-byte aligned multiples of 16 bytes between 256 "
+                          "and 8192 bytes, else gather_rows_kernel (features._CAPI_index_counted = "
+                          "dgs_gather_rows_counted, what BlockPipeline queues per batch)",
+                "ms_per_launch": ms_counted, "achieved": bytes_of / (ms_counted * 1e-3) / 1e9,
+                "frac": bytes_of / (ms_counted * 1e-3) / 1e9 / peak},
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "peak_kind": {"hbm": hbm_kind + " (MEASURED_PEAKS.json hbm_gbs)", "nvlink": peaks.get("nvlink_kind"),
                           "host": "measured: pinned host->device copy of 256 MiB, best of 6"}[bound],

@@ -103,6 +103,29 @@ class ChunkTensor : public torch::CustomClassHolder {
   torch::Tensor RemoteIndex(torch::Tensor index) { return IndexClass(index, DGS_CLASS_REMOTE, "_CAPI_remote_index"); }
   torch::Tensor HostIndex(torch::Tensor index) { return IndexClass(index, DGS_CLASS_HOST, "_CAPI_host_index"); }
 
+  // _CAPI_index with the number of rows taken from the device: out[i] = row index[i] for i < count[0], where
+  // `count` is an int64 CUDA tensor written by earlier work on the stream (clamped to index.numel()); the rest
+  // of `out` [index.numel(), D] is left as it is.  For callers that queue a gather behind a kernel that
+  // produces the ids without reading their number back; the form BlockPipeline uses per batch
+  // (dgs_gather_rows_counted).  No counterpart in src/chunk_tensor.h.
+  torch::Tensor IndexCounted(torch::Tensor index, torch::Tensor count) {
+    CHECK_CUDA(index);
+    CHECK_CUDA(count);
+    TORCH_CHECK(count.scalar_type() == torch::kInt64 && count.numel() >= 1 && count.device() == index.device(),
+                "_CAPI_index_counted: count must be an int64 tensor on the device of index");
+    const bool ids64 = is_id64(index, "index");
+    c10::cuda::CUDAGuard guard(index.device());
+    const Lease lease("_CAPI_index_counted", index.device().index(), current_stream());
+    index = index.contiguous();
+    const int64_t n = index.numel();
+    torch::Tensor out =
+        torch::empty({n, elem_stride_}, torch::TensorOptions().dtype(dtype_).device(index.device()));
+    DGS_CHECK_RC(dgs_gather_rows_counted(&desc_, index.data_ptr(), ids64, n, count.data_ptr<int64_t>(), elem_stride_,
+                                         out.data_ptr(), lease.status(), current_stream()));
+    lease.finish();
+    return out;
+  }
+
   std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> SplitIndex(torch::Tensor index) {
     CHECK_CUDA(index);
     const bool ids64 = is_id64(index, "index");

@@ -475,7 +475,9 @@ TORCH_LIBRARY(dgs_classes, m) {
       .def("_CAPI_local_index", &ChunkTensor::LocalIndex)
       .def("_CAPI_remote_index", &ChunkTensor::RemoteIndex)
       .def("_CAPI_host_index", &ChunkTensor::HostIndex)
-      .def("_CAPI_load_from_tensor", &ChunkTensor::LoadFromTensor);
+      .def("_CAPI_load_from_tensor", &ChunkTensor::LoadFromTensor)
+      // addition (no counterpart in src/pybind.cc): the gather with its row count on the device
+      .def("_CAPI_index_counted", &ChunkTensor::IndexCounted);
   // addition (no counterpart in src/pybind.cc): mini-batches in flight, see pipeline.h
   m.class_<BlockPipeline>("BlockPipeline")
       .def(torch::init<c10::intrusive_ptr<ChunkTensor>, c10::intrusive_ptr<ChunkTensor>,

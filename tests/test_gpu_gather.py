@@ -199,3 +199,24 @@ def test_chunktensor_class_features(ops, oracle):
     with pytest.raises(RuntimeError, match="out-of-range"):
         c._CAPI_index(torch.tensor([1], device="cuda"))
     assert c._CAPI_index(torch.tensor([1], device="cuda")).cpu().numpy().tobytes() == table[1].tobytes()
+
+
+def test_chunktensor_index_counted(ops):
+    """_CAPI_index_counted: the row count is an int64 word on the device; rows past it are left untouched,
+    a count beyond the request is clamped; 512-byte rows take the bulk-copy form, 36-byte rows the other."""
+    rng = np.random.default_rng(9)
+    for D in (128, 9):
+        table = rng.standard_normal((6000, D)).astype(np.float32)
+        c = torch.classes.dgs_classes.ChunkTensor([6000, D], torch.float32, 4 * D * 4000)   # 2 000 rows on the host
+        c._CAPI_load_from_tensor(torch.from_numpy(table))
+        idx = torch.from_numpy(rng.integers(0, 6000, size=5000)).cuda()
+        whole = c._CAPI_index(idx)
+        for live in (0, 1, 777, 5000, 9999):
+            count = torch.tensor([live], dtype=torch.int64, device="cuda")
+            out = c._CAPI_index_counted(idx, count)
+            n = min(live, 5000)
+            assert out.shape == (5000, D) and torch.equal(out[:n], whole[:n])
+        with pytest.raises(RuntimeError, match="int64"):
+            c._CAPI_index_counted(idx, torch.tensor([5], dtype=torch.int32, device="cuda"))
+        del c
+
