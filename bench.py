@@ -2,7 +2,7 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                   [--workload products|papers100m|friendster|small] [--batch 1024] [--weighted] [--scale F]
-                  [--api pipeline|blocks|per-hop] [--depth D]
+                  [--api pipeline|blocks|per-hop] [--depth D] [--consumer-stream high|default]
 
 One step = one mini-batch per rank:
   frontier, blocks = sample_blocks(seeds, [15, 10, 5])      # sample + relabel, fan-outs applied last to first
@@ -29,9 +29,10 @@ Printed JSON (rank 0, one line):
   value        sampled edges/s of the whole job, device-timed, seeds resident in HBM; step = sample + relabel + gather
   e2e          same metric with every batch's seeds coming from pinned host memory and a device->host read of the
                step's checksum inside the timed region (the result itself stays on the device, as in the
-               reference's API); e2e_full_d2h: the variant that copies input nodes, blocks and features to
+               reference's API); the consumer -- two reduction kernels and the copy -- runs on a high-priority
+               stream, `--consumer-stream default` puts it on a default-priority one; e2e_full_d2h: the variant that copies input nodes, blocks and features to
                pinned host buffers every step
-  roofline     the gather kernel: bytes of the binding class / CUDA-event time of back-to-back launches on the
+  roofline     the gather kernel (`pipeline_form`: the same through the call the pipeline makes): bytes of the binding class / CUDA-event time of back-to-back launches on the
                last frontiers, against that class's peak -- local HBM at N = 1, NVLink at N > 1 -- with the
                per-class bytes and the time-weighted bound t_min = max(B_hbm/BW_hbm, B_nvl/BW_nvl, B_host/BW_host)
   verified     one untimed batch checked on the device: counts = min(deg, k), every (row, col) an edge of the
@@ -116,6 +117,8 @@ def parse_args():
                     help="which of the three ways through the library is the headline `value`; the other two are "
                          "timed too and reported under other_api")
     ap.add_argument("--depth", type=int, default=6, help="batches in flight in the pipeline")
+    ap.add_argument("--consumer-stream", default="high", choices=["high", "default"],
+                    help="priority of the stream the e2e consumer (checksum kernels, copies) runs on")
     ap.add_argument("--no-extra-configs", action="store_true",
                     help="skip the short Papers100M-shaped measurement at the end of a default run")
     ap.add_argument("--extra-steps", type=int, default=200, help="timed steps of that extra measurement")
@@ -654,7 +657,7 @@ def measure_workload(env, args, pkg, wl, steps, warmup, full):
     chk_host = torch.zeros((64, 2), dtype=torch.float32).pin_memory()
     chk_dev = torch.zeros(2, dtype=torch.float32, device=dev)
     chk_state = {"i": 0}
-    consumer_stream = torch.cuda.Stream(device=dev, priority=-1)
+    consumer_stream = torch.cuda.Stream(device=dev, priority=-1 if args.consumer_stream == "high" else 0)
 
     def checksum(fr, blocks, x):
         # 8 bytes leave the device every step, into a ring of pinned words: a checksum of the last 1 024
@@ -929,7 +932,8 @@ def main_ours(args):
                     "result_left_on_device": True,
                     "what": "pipeline; every batch's seeds copied from pinned host memory; a checksum of the last "
                             "1 024 gathered feature rows and input nodes plus the sizes read back every step; the "
-                            "consumer (checksum kernels, copies) runs on a high-priority stream"},
+                            "consumer (checksum kernels, copies) runs on a %s-priority stream"
+                            % args.consumer_stream},
             "e2e_full_d2h": {"value": red["e2e_full"]["edges_all"] / (red["e2e_full"]["ms"] * 1e-3), "unit": "edges/s",
                              "ms_per_step": red["e2e_full"]["ms"] / args.steps,
                              "h2d_bytes_per_step": args.batch * 8,
