@@ -271,14 +271,17 @@ class PipelinedSampler:
     batches are tensors on the GPU or in (pinned) host memory, at most max_seeds ids each.  Results follow
     the same rules as sample_blocks(): identical wherever no random choice is involved.
     Delete the sampler before the ChunkTensors it reads (their destructor is collective).
+    src_nodes: the size of the id space `indices` draws from when that is larger than indptr's node count
+    (a bipartite CSC); the buffers for the input nodes are sized by it.
     """
 
-    def __init__(self, indptr, indices, fanouts, features=None, probs=None, replace=False, max_seeds=1024, depth=6):
+    def __init__(self, indptr, indices, fanouts, features=None, probs=None, replace=False, max_seeds=1024, depth=6,
+                 src_nodes=0):
         import torch
         load_ops()
         self.depth = int(depth)
         self.pipe = torch.classes.dgs_classes.BlockPipeline(indptr, indices, probs, features, list(fanouts),
-                                                            bool(replace), int(max_seeds), self.depth)
+                                                            bool(replace), int(max_seeds), self.depth, int(src_nodes))
 
     def submit(self, seeds):
         self.pipe.submit(seeds)

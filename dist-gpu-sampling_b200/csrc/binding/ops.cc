@@ -282,8 +282,9 @@ BlocksResult blocks_impl(torch::Tensor seeds, const dgs_chunk_desc& indptr, torc
     sequence = total <= kBlocksBudgetBytes;
   }
 
-  if (!sequence) {
-    // hop by hop through the per-operator path (empty input, zero fan-outs, very large bounds)
+  // hop by hop through the per-operator path: empty input, zero fan-outs, very large bounds, or a frontier
+  // that outgrew the bound of the one-sequence path (see below)
+  auto hop_by_hop = [&]() -> BlocksResult {
     torch::Tensor cur = seeds;
     for (int h = 0; h < H; ++h) {
       auto rc = sample_impl(cur, indptr, indptr_dtype, indices, indices_dtype, probs, applied[h], replace);
@@ -296,7 +297,8 @@ BlocksResult blocks_impl(torch::Tensor seeds, const dgs_chunk_desc& indptr, torc
       cur = std::get<0>(rl);
     }
     return std::make_tuple(cur, rows, cols, shape);
-  }
+  };
+  if (!sequence) return hop_by_hop();
 
   auto opt = seeds.options();
   cudaStream_t stream = current_stream();
@@ -318,11 +320,27 @@ BlocksResult blocks_impl(torch::Tensor seeds, const dgs_chunk_desc& indptr, torc
                                  rng.second, ws.data_ptr(), ws_bytes, w.sizes(), w.status(), stream));
   // the one read-back: the last size lands while that hop's numbering and lookup still run
   int64_t n_dst = n;
+  bool outgrown = false;
   for (int h = 0; h < H; ++h) {
     const int64_t nnz = wait_size(w.sizes() + 2 * h, stream, "sample_blocks");
     const int64_t nu = wait_size(w.sizes() + 2 * h + 1, stream, "sample_blocks");
     TORCH_CHECK(nnz >= 0 && nnz <= hops[h].seed_bound * hops[h].fanout && nu >= 0,
                 "dgs: sample_blocks returned an impossible size");
+    outgrown = outgrown || nu > hops[h].frontier_bound;
+  }
+  if (outgrown) {
+    // The bound assumes that neighbour ids lie in indptr's node space.  On a bipartite CSC whose column ids
+    // live in a larger space a hop can find more distinct ids than indptr has rows; the per-hop operators have
+    // no such assumption, so the batch is run again through them.  The out-of-range status the numbering
+    // kernel raised for the cut-off frontier belongs to the bound, not to the caller's input.
+    sync_stream();
+    if (*w.status() == DGS_ERR_RANGE) *w.status() = 0;
+    w.check();
+    for (int h = 0; h < H; ++h) rows[h] = cols[h] = torch::Tensor();
+    return hop_by_hop();
+  }
+  for (int h = 0; h < H; ++h) {
+    const int64_t nnz = w.sizes()[2 * h], nu = w.sizes()[2 * h + 1];
     const int at = H - 1 - h;
     rows[at] = rows[at].narrow(0, 0, nnz);
     cols[at] = cols[at].narrow(0, 0, nnz);
@@ -482,7 +500,7 @@ TORCH_LIBRARY(dgs_classes, m) {
   m.class_<BlockPipeline>("BlockPipeline")
       .def(torch::init<c10::intrusive_ptr<ChunkTensor>, c10::intrusive_ptr<ChunkTensor>,
                        c10::optional<c10::intrusive_ptr<ChunkTensor>>, c10::optional<c10::intrusive_ptr<ChunkTensor>>,
-                       std::vector<int64_t>, bool, int64_t, int64_t>())
+                       std::vector<int64_t>, bool, int64_t, int64_t, int64_t>())
       .def("submit", &BlockPipeline::submit)
       .def("next", &BlockPipeline::next)
       .def("pending", &BlockPipeline::pending)

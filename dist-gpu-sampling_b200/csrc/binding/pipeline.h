@@ -72,7 +72,7 @@ class BlockPipeline : public torch::CustomClassHolder {
   BlockPipeline(c10::intrusive_ptr<ChunkTensor> indptr, c10::intrusive_ptr<ChunkTensor> indices,
                 c10::optional<c10::intrusive_ptr<ChunkTensor>> probs,
                 c10::optional<c10::intrusive_ptr<ChunkTensor>> features, std::vector<int64_t> fanouts,
-                bool replace, int64_t max_seeds, int64_t depth)
+                bool replace, int64_t max_seeds, int64_t depth, int64_t src_nodes)
       : indptr_(std::move(indptr)), indices_(std::move(indices)), replace_(replace), max_seeds_(max_seeds) {
     if (probs.has_value() && probs.value().defined()) probs_ = probs.value();
     if (features.has_value() && features.value().defined()) features_ = features.value();
@@ -87,12 +87,16 @@ class BlockPipeline : public torch::CustomClassHolder {
     TORCH_CHECK(!probs_.defined() || probs_->dtype() == torch::kFloat, "probs must be float32");
     ids64_ = indptr_->dtype() == torch::kInt64;
     device_ = indptr_->device();
+    // A frontier cannot hold more distinct ids than the id space has.  That space is indptr's node count
+    // unless the caller says that `indices` holds ids of a larger one (a bipartite CSC): src_nodes.
+    TORCH_CHECK(src_nodes >= 0, "BlockPipeline: src_nodes must be >= 0 (0: the node count of indptr)");
+    id_space_ = std::max<int64_t>(indptr_->desc().total - 1, src_nodes);
     // the reference applies the fan-outs last to first (chunktensor_sampler.py:97)
     applied_.assign(fanouts.rbegin(), fanouts.rend());
 
     c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
     dgs_hop hops[DGS_MAX_HOPS];
-    DGS_CHECK_RC(dgs_sample_blocks_bounds(max_seeds_, applied_.data(), H_, indptr_->desc().total - 1, hops));
+    DGS_CHECK_RC(dgs_sample_blocks_bounds(max_seeds_, applied_.data(), H_, id_space_, hops));
     ws_bytes_ = dgs_sample_blocks_workspace_bytes(hops, H_);
     const int64_t esz = ids64_ ? 8 : 4;
     int64_t slot_bytes = static_cast<int64_t>(ws_bytes_) + max_seeds_ * esz;
@@ -262,6 +266,16 @@ class BlockPipeline : public torch::CustomClassHolder {
         const int64_t nnz = wait_size(s.sizes + 2 * h, s.stream, "BlockPipeline.next");
         const int64_t nu = wait_size(s.sizes + 2 * h + 1, s.stream, "BlockPipeline.next");
         TORCH_CHECK(nnz >= 0 && nnz <= s.edge_bound[h] && nu >= 0, "dgs: BlockPipeline returned an impossible size");
+        if (nu > s.frontier_bound[h]) {
+          // more distinct ids than the id space was said to have: the frontier was cut off
+          cudaEventSynchronize(s.done);
+          *s.status = 0;
+          ++tail_;
+          --in_flight_;
+          TORCH_CHECK(false, "dgs: BlockPipeline batch ", s.batch, ": hop ", h, " found ", nu, " distinct ids, more than the ",
+                      s.frontier_bound[h], " the id space allows; if `indices` holds ids beyond indptr's node count "
+                      "(a bipartite graph), pass that id space as src_nodes");
+        }
         const int at = H_ - 1 - h;
         rows[at] = s.rows[h].narrow(0, 0, nnz);
         cols[at] = s.cols[h].narrow(0, 0, nnz);
@@ -350,7 +364,7 @@ class BlockPipeline : public torch::CustomClassHolder {
       TORCH_CHECK(cudaStreamWaitEvent(s.stream, s.ready, 0) == cudaSuccess,
                   "BlockPipeline: cannot order the slot's stream after the caller's stream");
       dgs_hop hops[DGS_MAX_HOPS];
-      DGS_CHECK_RC(dgs_sample_blocks_bounds(n, applied_.data(), H_, indptr_->desc().total - 1, hops));
+      DGS_CHECK_RC(dgs_sample_blocks_bounds(n, applied_.data(), H_, id_space_, hops));
       for (int h = 0; h < H_; ++h) {
         hops[h].coo_row = s.rows[h].data_ptr();
         hops[h].coo_col = s.cols[h].data_ptr();
@@ -421,7 +435,7 @@ class BlockPipeline : public torch::CustomClassHolder {
   bool replace_ = false, ids64_ = true, record_ = true;
   int H_ = 0;
   int device_ = 0;
-  int64_t max_seeds_ = 0;
+  int64_t max_seeds_ = 0, id_space_ = 0;
   size_t ws_bytes_ = 0;
   int64_t edge_cap_[DGS_MAX_HOPS] = {0}, frontier_cap_[DGS_MAX_HOPS] = {0};
   std::vector<Slot> slots_;

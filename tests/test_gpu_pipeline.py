@@ -155,6 +155,55 @@ def test_pipeline_edge_cases_and_errors(ops, oracle, pkg):
     del sampler
 
 
+def test_bipartite_graph_whose_column_ids_exceed_the_row_count(ops, oracle, pkg):
+    """A CSC with 400 rows whose neighbour ids live in [0, 9000): one hop finds far more distinct ids than
+    indptr has rows.  The one-sequence operator notices the outgrown frontier and gives the per-hop result;
+    the pipeline needs the id space stated (src_nodes) and says so otherwise."""
+    rng = np.random.default_rng(41)
+    deg = rng.integers(5, 60, size=400)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, 9000, size=int(indptr[-1])).astype(np.int64)
+    indices[:400] = np.arange(400)                         # some ids inside the row space as well
+    seeds = rng.permutation(400)[:300]
+    fanouts = [20]
+
+    def check(f, blocks, ne):
+        (r, c, n_src, n_dst), = blocks
+        fr = f.cpu().numpy()
+        assert n_dst == 300 and n_src == fr.size and fr.size > 400 and np.unique(fr).size == fr.size
+        assert np.array_equal(fr[:300], seeds)
+        cnt = np.minimum(deg[seeds], 20)
+        assert ne == cnt.sum() and np.array_equal(fr[r.cpu().numpy()], np.repeat(seeds, cnt))
+        cols = fr[c.cpu().numpy()]
+        at = 0
+        for s_, k_ in zip(seeds, cnt):
+            row = indices[indptr[s_]:indptr[s_ + 1]]
+            assert np.isin(cols[at:at + k_], row).all()
+            at += k_
+        assert fr.max() >= 400
+
+    ip, ix, sd = to_dev(indptr), to_dev(indices), to_dev(seeds)
+    f, blocks, ne = pkg.sample_blocks(sd, fanouts, ip, ix, fused=True)
+    check(f, blocks, ne)
+    # the next call is not blamed for the cut-off frontier of the first attempt
+    f, blocks, ne = pkg.sample_blocks(sd, fanouts, ip, ix, fused=True)
+    check(f, blocks, ne)
+
+    c_ip, c_ix = chunked(indptr), chunked(indices)
+    sampler = pkg.PipelinedSampler(c_ip, c_ix, fanouts, max_seeds=300, depth=2, src_nodes=9000)
+    for f, blocks, ne, _ in sampler([sd, sd, sd]):
+        check(f, blocks, ne)
+    del sampler
+    sampler = pkg.PipelinedSampler(c_ip, c_ix, fanouts, max_seeds=300, depth=2)
+    sampler.submit(sd)
+    with pytest.raises(RuntimeError, match="src_nodes"):
+        sampler.next()
+    sampler.submit(to_dev(np.arange(5)))                   # the pipeline stays usable
+    f, blocks, ne, _ = sampler.next()
+    assert ne == int(np.minimum(deg[:5], 20).sum())
+    del sampler
+
+
 def test_two_operator_calls_in_flight_on_two_streams(ops, oracle, pkg):
     """Two host threads, each on its own stream, call _CAPI_sample_blocks and the per-hop operators at the
     same time: each call leases its own pinned size / status words, so neither sees the other's sizes."""
